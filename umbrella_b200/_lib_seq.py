@@ -1,0 +1,109 @@
+"""ctypes binding of libumbrella_b200_seq.so (the C ABI declared in include/umbrella_b200_seq.h): the batched step
+of the sequence-state decoders and its building blocks.
+
+The library is compiled in-tree on first use when it is missing or older than its sources (``build.build_seq``: three
+small translation units, seconds) -- a fresh checkout serves these models without a separate build step.  There is
+no PyTorch / CPU fallback behind these calls: without nvcc and without the library, loading is an error.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from ._lib import c_float, c_int, c_int64, c_size_t, c_void_p
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libumbrella_b200_seq.so")
+
+UMBS_BF16, UMBS_F32 = 0, 1
+UMBS_MIX_RETENTION, UMBS_MIX_LATENT_ATTENTION = 0, 1
+
+
+class Batch(C.Structure):
+    _fields_ = [("n_tokens", c_int), ("n_seqs", c_int), ("n_want", c_int), ("max_seq_len", c_int),
+                ("tok_ids", c_void_p), ("tok_seq", c_void_p), ("tok_pos", c_void_p), ("seq_slot", c_void_p),
+                ("seq_start", c_void_p), ("seq_len", c_void_p), ("seq_pos0", c_void_p), ("seq_parity", c_void_p),
+                ("want_rows", c_void_p)]
+
+
+class Mlp(C.Structure):
+    _fields_ = [("experts", c_int), ("top", c_int), ("ff", c_int), ("limit", c_float), ("w_router", c_void_p),
+                ("w_gu", c_void_p), ("w_down", c_void_p), ("shared_ff", c_int), ("shared_limit", c_float),
+                ("ws_gu", c_void_p), ("ws_down", c_void_p)]
+
+
+class Layer(C.Structure):
+    _fields_ = [("mixer", c_int), ("heads", c_int), ("dim", c_int), ("vdim", c_int),
+                ("rot_dims", c_int), ("inv_freq", c_void_p), ("decay", c_void_p), ("ret_state", c_void_p),
+                ("q_rank", c_int), ("kv_rank", c_int), ("window", c_int), ("ring_len", c_int), ("scale", c_float),
+                ("q_norm", c_void_p), ("kv_norm", c_void_p), ("w_uq", c_void_p), ("w_ukT", c_void_p), ("w_uv", c_void_p),
+                ("ring", c_void_p),
+                ("w_in", c_void_p), ("w_o", c_void_p), ("norm_w", c_void_p), ("shift_w", c_void_p),
+                ("shift_state", c_void_p), ("depth_w", c_void_p), ("has_mlp", c_int), ("mlp", Mlp)]
+
+
+class Model(C.Structure):
+    _fields_ = [("dtype", c_int), ("width", c_int), ("vocab", c_int), ("n_layers", c_int), ("norm_groups", c_int),
+                ("slots", c_int), ("norm_eps", c_float), ("embed", c_void_p), ("final_norm", c_void_p), ("head", c_void_p),
+                ("layers", C.POINTER(Layer))]
+
+
+_BP = C.POINTER(Batch)
+# name -> (restype, argtypes); lists every symbol include/umbrella_b200_seq.h declares
+SIGNATURES = {
+    "umbs_version": (C.c_char_p, []),
+    "umbs_launch_count": (C.c_ulonglong, []),
+    "umbs_workspace_bytes": (c_size_t, [C.POINTER(Model), c_int, c_int]),
+    "umbs_forward": (c_int, [C.POINTER(Model), _BP, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "umbs_gemm": (c_int, [c_int, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int, c_int,
+                          c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p]),
+    "umbs_group_norm_shift": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, _BP, c_int, c_int, c_float,
+                                      c_void_p, c_void_p, c_void_p]),
+    "umbs_group_norm_rows": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p]),
+    "umbs_retention": (c_int, [c_int, c_void_p, c_int64, _BP, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                               c_void_p, c_void_p, c_void_p, c_void_p]),
+    "umbs_latent_norm": (c_int, [c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                 c_void_p]),
+    "umbs_latent_attention": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, _BP, c_int, c_int, c_int, c_float,
+                                      c_void_p, c_void_p]),
+    "umbs_ring_append": (c_int, [c_int, c_void_p, c_void_p, c_int, _BP, c_int, c_void_p]),
+    "umbs_moe_route": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_void_p, c_void_p]),
+    "umbs_depth_mix": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "umbs_embedding": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the library (once), compiling it first when it is missing or stale and nvcc is there."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    from . import build
+    try:
+        build.build_seq()
+    except RuntimeError:
+        if not os.path.exists(LIB_PATH):
+            raise
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(rc: int, what: str = "") -> None:
+    if rc != 0:
+        from . import _lib as core
+        msg = {-1: "invalid argument", -2: "shape or option not supported", -3: "workspace too small"}.get(rc)
+        if msg is None:
+            try:
+                msg = core.load().umb_error_string(rc).decode()
+            except Exception:
+                msg = "CUDA error"
+        raise RuntimeError(f"umbrella_b200_seq {what} failed: status {rc} ({msg})")

@@ -1,0 +1,95 @@
+"""Slot-based state of the sequence-state decoders (the counterpart of attn/cache.py's KV_Cache for models whose
+per-sequence memory does not grow with the context).
+
+Every live sequence owns one slot.  A slot holds, per layer,
+  * token shift: the previous token's normed activations, fp32 [width], double-buffered (a step reads the half
+    ``parity`` names and writes the other, then the parity flips);
+  * retention layers: the state matrices, fp32 [heads, dim, vdim];
+  * latent-attention layers: a ring of the last ``ring_len`` latents, [ring_len, kv_rank] in the activation dtype,
+    position p at row p mod ring_len (ring_len = the layer's window, capped by ``max_length`` when that is given).
+and on the host its position (tokens fed so far) and parity.  Nothing is cleared when a slot is freed or handed out
+again: the kernels read a sequence's state as zero while its position is 0, and a ring row is only ever read for a
+position that the current owner has written.
+"""
+from __future__ import annotations
+
+import torch
+
+
+class SequenceStateCache:
+    def __init__(self, spec, slots: int = 8, device="cuda:0", dtype=torch.bfloat16, max_length: int | None = None):
+        self.spec, self.device, self.dtype = spec, torch.device(device), dtype
+        self.max_length = max_length
+        self.slots = 0
+        self.shift: list[torch.Tensor | None] = [None] * len(spec.layers)
+        self.ret_state: list[torch.Tensor | None] = [None] * len(spec.layers)
+        self.ring: list[torch.Tensor | None] = [None] * len(spec.layers)
+        self.position: list[int] = []
+        self.parity: list[int] = []
+        self._free: list[int] = []
+        self.version = 0                      # bumped whenever the tensors are reallocated (pointers change)
+        self.grow(max(1, int(slots)))
+
+    def ring_len(self, layer) -> int:
+        n = int(layer.window)
+        return max(1, min(n, self.max_length) if self.max_length else n)
+
+    def grow(self, slots: int):
+        """Make room for ``slots`` slots, keeping what the existing ones hold."""
+        if slots <= self.slots:
+            return
+        old = self.slots
+        f32 = dict(dtype=torch.float32, device=self.device)
+
+        def widen(t_old, shape, slot_dim, **kw):
+            t = torch.zeros(shape, **kw)
+            if t_old is not None:
+                t.narrow(slot_dim, 0, old).copy_(t_old)
+            return t
+        for i, l in enumerate(self.spec.layers):
+            if l.shift:
+                self.shift[i] = widen(self.shift[i], (2, slots, self.spec.width), 1, **f32)
+            if l.mixer == "retention":
+                self.ret_state[i] = widen(self.ret_state[i], (slots, l.heads, l.dim, l.vdim), 0, **f32)
+            elif l.mixer == "latent_attention":
+                self.ring[i] = widen(self.ring[i], (slots, self.ring_len(l), l.kv_rank), 0, dtype=self.dtype,
+                                     device=self.device)
+        self.position += [0] * (slots - old)
+        self.parity += [0] * (slots - old)
+        self._free += list(range(old, slots))
+        self.slots = slots
+        self.version += 1
+
+    def alloc_slot(self) -> int:
+        """A slot for a new sequence (position 0).  Grows the cache when every slot is taken."""
+        if not self._free:
+            self.grow(self.slots * 2)
+        s = self._free.pop(0)
+        self.position[s], self.parity[s] = 0, 0
+        return s
+
+    def free_slot(self, slot: int):
+        if slot in self._free or not 0 <= slot < self.slots:
+            raise ValueError(f"slot {slot} is not in use")
+        self.position[slot] = 0
+        self._free.append(slot)
+
+    @property
+    def live_slots(self) -> int:
+        return self.slots - len(self._free)
+
+    def advance(self, slot: int, n_tokens: int):
+        self.position[slot] += n_tokens
+        self.parity[slot] ^= 1
+
+    def state_bytes_per_slot(self) -> int:
+        n = 0
+        for t in self.shift + self.ret_state + self.ring:
+            if t is not None:
+                n += t.numel() * t.element_size() // self.slots
+        return n
+
+    def clear(self):
+        self._free = list(range(self.slots))
+        self.position = [0] * self.slots
+        self.parity = [0] * self.slots

@@ -1,0 +1,181 @@
+// umbs_forward: one batched step of a sequence-state decoder -- the chain of launches for every layer, enqueued on
+// the caller's stream from one C call, over a workspace carved up here.
+#include <atomic>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "seq_internal.h"
+
+namespace umbs {
+static std::atomic<unsigned long long> g_launches{0};
+void count_launches(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+struct Arena {
+    char* base;
+    size_t used, cap;
+    void* take(size_t bytes) {
+        used = (used + 255) & ~(size_t)255;
+        void* p = base ? base + used : nullptr;
+        used += bytes;
+        return p;
+    }
+};
+
+struct Scratch {
+    float* stack;      // [L + 1, T, width]   X_0 .. X_L
+    float* x;          // [T, width]          what the next layer reads (depth-mixed)
+    void* h;           // act [T, width]
+    void* hs;          // act [T, width]
+    float* proj;       // fp32 [T, max in-projection rows]
+    float* o32;        // fp32 [T, max(heads vdim)]  retention outputs before the gate
+    void* mixed;       // act [T, max(heads vdim)]   mixer output before W_o
+    void* cq;          // act [T, max q_rank]
+    void* c;           // act [T, max kv_rank]
+    void* q;           // act [T, max heads dim]
+    float* q_abs;      // fp32 [T, max heads kv_rank]
+    void* o_lat;       // act [T, max heads kv_rank]
+    float* mix_out;    // fp32 [T, width]
+    float* sel_w;      // fp32 [T, max top]
+    int32_t* grp_off;  // [max experts + 1]
+    int32_t* pair_tok; // [T max top]
+    int32_t* pair_pos; // [T max top]
+    int32_t* route_scratch;   // [2 max experts + T max top]
+    void* y;           // act [T max top, max ff]
+    float* pair_out;   // fp32 [T max top, width]
+    void* ys;          // act [T, max shared ff]
+    float* shared_out; // fp32 [T, width]
+    void* final_h;     // act [n_want, width]
+};
+
+static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratch* s) {
+    const size_t es = m->dtype == UMBS_F32 ? 4 : 2;
+    int in_rows = 1, hv = 1, qr = 1, kvr = 1, hd = 1, hkv = 1, top = 1, experts = 1, ff = 1, sff = 1;
+    for (int i = 0; i < m->n_layers; ++i) {
+        const umbs_layer_t& l = m->layers[i];
+        auto up = [](int& a, int b) { if (b > a) a = b; };
+        up(hv, l.heads * l.vdim);
+        if (l.mixer == UMBS_MIX_RETENTION) up(in_rows, 2 * l.heads * l.dim + 2 * l.heads * l.vdim);
+        else {
+            up(in_rows, l.q_rank + l.kv_rank);
+            up(qr, l.q_rank); up(kvr, l.kv_rank); up(hd, l.heads * l.dim); up(hkv, l.heads * l.kv_rank);
+        }
+        if (l.has_mlp) { up(top, l.mlp.top); up(experts, l.mlp.experts); up(ff, l.mlp.ff); up(sff, l.mlp.shared_ff); }
+    }
+    Arena a{base, 0, 0};
+    const size_t W = m->width, Tz = T;
+    Scratch z;
+    z.stack = (float*)a.take((size_t)(m->n_layers + 1) * Tz * W * 4);
+    z.x = (float*)a.take(Tz * W * 4);
+    z.h = a.take(Tz * W * es);
+    z.hs = a.take(Tz * W * es);
+    z.proj = (float*)a.take(Tz * in_rows * 4);
+    z.o32 = (float*)a.take(Tz * hv * 4);
+    z.mixed = a.take(Tz * hv * es);
+    z.cq = a.take(Tz * qr * es);
+    z.c = a.take(Tz * kvr * es);
+    z.q = a.take(Tz * hd * es);
+    z.q_abs = (float*)a.take(Tz * hkv * 4);
+    z.o_lat = a.take(Tz * hkv * es);
+    z.mix_out = (float*)a.take(Tz * W * 4);
+    z.sel_w = (float*)a.take(Tz * top * 4);
+    z.grp_off = (int32_t*)a.take((size_t)(experts + 1) * 4);
+    z.pair_tok = (int32_t*)a.take(Tz * top * 4);
+    z.pair_pos = (int32_t*)a.take(Tz * top * 4);
+    z.route_scratch = (int32_t*)a.take((2 * (size_t)experts + Tz * top) * 4);
+    z.y = a.take(Tz * top * ff * es);
+    z.pair_out = (float*)a.take(Tz * top * W * 4);
+    z.ys = a.take(Tz * sff * es);
+    z.shared_out = (float*)a.take(Tz * W * 4);
+    z.final_h = a.take((size_t)(n_want > 0 ? n_want : 1) * W * es);
+    if (s) *s = z;
+    return a.used + 256;
+}
+}  // namespace umbs
+
+using namespace umbs;
+
+extern "C" const char* umbs_version(void) { return "umbrella_b200_seq 0.1 (sm_100a)"; }
+extern "C" unsigned long long umbs_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+extern "C" size_t umbs_workspace_bytes(const umbs_model_t* model, int max_tokens, int max_want) {
+    if (model == nullptr || max_tokens <= 0) return 0;
+    return carve(model, max_tokens, max_want, nullptr, nullptr);
+}
+
+#define UMBS_TRY(expr) do { int rc__ = (expr); if (rc__ != 0) return rc__; } while (0)
+
+extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float* logits, float* layer_out, void* workspace,
+                            size_t workspace_bytes, umbs_stream_t stream) {
+    if (m == nullptr || b == nullptr || workspace == nullptr) return UMB_ERR_ARG;
+    const int T = b->n_tokens, W = m->width, dt = m->dtype;
+    if (T <= 0) return 0;
+    if ((uintptr_t)workspace % 256 != 0) return UMB_ERR_ARG;
+    Scratch s;
+    if (carve(m, T, b->n_want, (char*)workspace, &s) > workspace_bytes) return UMB_ERR_WORKSPACE;
+    const int64_t plane = (int64_t)T * W;
+    UMBS_TRY(umbs_embedding(dt, b->tok_ids, m->embed, s.stack, T, W, stream));
+    const float* x = s.stack;                    // layer 0 reads X_0 itself
+    for (int i = 0; i < m->n_layers; ++i) {
+        const umbs_layer_t& l = m->layers[i];
+        UMBS_TRY(umbs_group_norm_shift(dt, x, l.norm_w, l.shift_w, l.shift_state, m->slots, b, W, m->norm_groups,
+                                       m->norm_eps, s.h, l.shift_w ? s.hs : s.h, stream));
+        const void* hs = l.shift_w ? s.hs : s.h;
+        const int hv = l.heads * l.vdim;
+        if (l.mixer == UMBS_MIX_RETENTION) {
+            const int rows = 2 * l.heads * l.dim + 2 * hv;
+            UMBS_TRY(umbs_gemm(dt, hs, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
+            UMBS_TRY(umbs_retention(dt, s.proj, rows, b, l.heads, l.dim, l.vdim, l.rot_dims, l.inv_freq, l.decay,
+                                    m->norm_eps, l.ret_state, s.o32, s.mixed, stream));
+        } else if (l.mixer == UMBS_MIX_LATENT_ATTENTION) {
+            const int rows = l.q_rank + l.kv_rank, hd = l.heads * l.dim, R = l.kv_rank;
+            UMBS_TRY(umbs_gemm(dt, hs, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
+            UMBS_TRY(umbs_latent_norm(dt, s.proj, T, l.q_rank, R, l.q_norm, l.kv_norm, m->norm_eps, s.cq, s.c, stream));
+            UMBS_TRY(umbs_gemm(dt, s.cq, l.q_rank, 0, l.w_uq, l.q_rank, 0, s.q, hd, 0, 0, T, hd, l.q_rank, 1, nullptr, nullptr, 0,
+                               0.f, stream));
+            // q_abs[t, h, :] = W_uk[h]^T q[t, h, :]: scores against the cached latents need no per-key up-projection
+            UMBS_TRY(umbs_gemm(dt, s.q, hd, l.dim, l.w_ukT, l.dim, (int64_t)R * l.dim, s.q_abs, (int64_t)l.heads * R, R, 1, T, R,
+                               l.dim, l.heads, nullptr, nullptr, 0, 0.f, stream));
+            UMBS_TRY(umbs_latent_attention(dt, s.q_abs, s.c, l.ring, l.ring_len, b, l.heads, R, l.window, l.scale, s.o_lat,
+                                           stream));
+            UMBS_TRY(umbs_ring_append(dt, s.c, l.ring, l.ring_len, b, R, stream));
+            UMBS_TRY(umbs_gemm(dt, s.o_lat, (int64_t)l.heads * R, R, l.w_uv, R, (int64_t)l.vdim * R, s.mixed, hv, l.vdim, 0, T,
+                               l.vdim, R, l.heads, nullptr, nullptr, 0, 0.f, stream));
+        } else {
+            return UMB_ERR_UNSUPPORTED;
+        }
+        UMBS_TRY(umbs_gemm(dt, s.mixed, hv, 0, l.w_o, hv, 0, s.mix_out, W, 0, 1, T, W, hv, 1, nullptr, nullptr, 0, 0.f, stream));
+        const float* pair_out = nullptr;
+        const float* shared = nullptr;
+        int top = 0;
+        if (l.has_mlp) {
+            const umbs_mlp_t& f = l.mlp;
+            if (f.experts > 0) {
+                top = f.top;
+                UMBS_TRY(umbs_moe_route(dt, s.h, T, W, f.w_router, f.experts, f.top, s.sel_w, s.grp_off, s.pair_tok, s.pair_pos,
+                                        s.route_scratch, stream));
+                UMBS_TRY(umbs_gemm(dt, s.h, W, 0, f.w_gu, W, (int64_t)2 * f.ff * W, s.y, f.ff, 0, 0, T, f.ff, W, f.experts,
+                                   s.grp_off, s.pair_tok, 1, f.limit, stream));
+                UMBS_TRY(umbs_gemm(dt, s.y, f.ff, 0, f.w_down, f.ff, (int64_t)W * f.ff, s.pair_out, W, 0, 1, T, W, f.ff, f.experts,
+                                   s.grp_off, nullptr, 0, 0.f, stream));
+                pair_out = s.pair_out;
+            }
+            if (f.shared_ff > 0) {
+                UMBS_TRY(umbs_gemm(dt, s.h, W, 0, f.ws_gu, W, 0, s.ys, f.shared_ff, 0, 0, T, f.shared_ff, W, 1, nullptr, nullptr, 1,
+                                   f.shared_limit, stream));
+                UMBS_TRY(umbs_gemm(dt, s.ys, f.shared_ff, 0, f.ws_down, f.shared_ff, 0, s.shared_out, W, 0, 1, T, W, f.shared_ff, 1,
+                                   nullptr, nullptr, 0, 0.f, stream));
+                shared = s.shared_out;
+            }
+        }
+        UMBS_TRY(umbs_depth_mix(x, s.mix_out, pair_out, s.sel_w, s.pair_pos, top, shared, s.stack, i, l.depth_w, s.x,
+                                layer_out ? layer_out + (int64_t)i * plane : nullptr, T, W, stream));
+        x = s.x;
+    }
+    if (logits != nullptr && b->n_want > 0) {
+        UMBS_TRY(umbs_group_norm_rows(dt, x, b->want_rows, b->n_want, m->final_norm, W, m->norm_groups, m->norm_eps, s.final_h,
+                                      stream));
+        UMBS_TRY(umbs_gemm(dt, s.final_h, W, 0, m->head, W, 0, logits, m->vocab, 0, 1, b->n_want, m->vocab, W, 1, nullptr, nullptr, 0,
+                           0.f, stream));
+    }
+    return 0;
+}

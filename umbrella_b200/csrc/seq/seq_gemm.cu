@@ -1,0 +1,254 @@
+// Matrix products of the sequence-state decoders: C = A W^T with W stored [out, in], batched over groups (heads or
+// experts), optionally over expert-sorted gathered rows, optionally with the gated feed-forward activation fused
+// into the epilogue of a gate|up pair of products.
+//
+// Two kernels share one argument block:
+//   * gemm_simt_kernel  -- fp32 FMA chains over shared-memory tiles; the UMBS_F32 mode (true 32-bit) and every shape
+//                          the tensor-core kernel does not take (K not a multiple of 16, unaligned rows);
+//   * gemm_mma_kernel   -- bf16 operands through mma.sync.m16n8k16 with fp32 accumulators.
+// Both walk k from 0 upwards in one chain per output element, so a row's result is the same whatever else is in
+// the batch and however the prompt was cut.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "seq_internal.h"
+
+namespace umbs {
+
+struct GemmArgs {
+    const void* A; int64_t lda; int a_goff;
+    const void* W; int64_t ldw; int64_t w_gstride;
+    void* C; int64_t ldc; int c_goff;
+    int M, N, K;
+    const int32_t* grp_off;
+    const int32_t* row_src;
+    float limit;
+};
+
+__device__ __forceinline__ float gated_act(float g, float u, float limit) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * (1.f / (1.f + expf(-1.702f * g))) * (u + 1.f);
+}
+
+// ------------------------------------------------------------------------------------------------ SIMT
+constexpr int BM = 64, BN = 64, BK = 16;
+
+template <typename TA, typename TC, bool DUAL>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(GemmArgs a) {
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[DUAL ? 2 : 1][BK][BN + 4];
+    const int g = blockIdx.z;
+    int row_lo = 0, rows = a.M;
+    if (a.grp_off != nullptr) { row_lo = a.grp_off[g]; rows = a.grp_off[g + 1] - row_lo; }
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    if (m0 >= rows) return;
+    const TA* A = (const TA*)a.A + (int64_t)g * a.a_goff;
+    const TA* W = (const TA*)a.W + (int64_t)g * a.w_gstride;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    // loader mapping: 256 threads x 4 elements = a 64 x 16 tile; thread -> (row = tid / 4, k = (tid % 4) * 4 ..)
+    const int lr = tid >> 2, lk = (tid & 3) * 4;
+    int64_t a_row = -1;
+    if (m0 + lr < rows) {
+        const int p = row_lo + m0 + lr;
+        a_row = a.row_src ? a.row_src[p] : p;
+    }
+    const int wn = n0 + lr;
+    float acc[4][4] = {}, acc2[DUAL ? 4 : 1][4] = {};
+    for (int k0 = 0; k0 < a.K; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int k = k0 + lk + i;
+            As[lk + i][lr] = (a_row >= 0 && k < a.K) ? to_f32(A[a_row * a.lda + k]) : 0.f;
+            Ws[0][lk + i][lr] = (wn < a.N && k < a.K) ? to_f32(W[(int64_t)wn * a.ldw + k]) : 0.f;
+            if (DUAL) Ws[DUAL ? 1 : 0][lk + i][lr] = (wn < a.N && k < a.K) ? to_f32(W[(int64_t)(a.N + wn) * a.ldw + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float av[4], wv[4], wv2[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { av[i] = As[k][ty * 4 + i]; wv[i] = Ws[0][k][tx * 4 + i]; }
+            if (DUAL) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) wv2[i] = Ws[DUAL ? 1 : 0][k][tx * 4 + i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+                    if (DUAL) acc2[DUAL ? i : 0][j] = fmaf(av[i], wv2[j], acc2[DUAL ? i : 0][j]);
+                }
+        }
+        __syncthreads();
+    }
+    TC* C = (TC*)a.C + (int64_t)g * a.c_goff;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= a.N) continue;
+            const float v = DUAL ? gated_act(acc[i][j], acc2[DUAL ? i : 0][j], a.limit) : acc[i][j];
+            C[(int64_t)(row_lo + m) * a.ldc + n] = from_f32<TC>(v);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ bf16 tensor cores
+// 128 x 64 output tile per block of 256 threads (8 warps: 4 along m x 2 along n, 32 x 32 each), k in steps of 32
+// through a two-stage shared-memory ring filled with 16-byte loads.  Rows are padded to 40 halves so that the
+// fragment loads of a warp hit distinct banks.
+constexpr int TM = 128, TN = 64, TK = 32, TKP = TK + 8;
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <typename TC, bool DUAL>
+__global__ void __launch_bounds__(256) gemm_mma_kernel(GemmArgs a) {
+    __shared__ __align__(16) __nv_bfloat16 As[2][TM][TKP];
+    __shared__ __align__(16) __nv_bfloat16 Ws[2][DUAL ? 2 : 1][TN][TKP];
+    const int g = blockIdx.z;
+    int row_lo = 0, rows = a.M;
+    if (a.grp_off != nullptr) { row_lo = a.grp_off[g]; rows = a.grp_off[g + 1] - row_lo; }
+    const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+    if (m0 >= rows) return;
+    const __nv_bfloat16* A = (const __nv_bfloat16*)a.A + (int64_t)g * a.a_goff;
+    const __nv_bfloat16* W = (const __nv_bfloat16*)a.W + (int64_t)g * a.w_gstride;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wm = (warp & 3) * 32, wn = (warp >> 2) * 32;
+    // loaders: A tile 128 rows x 4 16-byte pieces = 512 pieces, two per thread; W tile 64 x 4 = 256, one per thread
+    const int pr = tid >> 2, pc = (tid & 3) * 8;
+    int64_t arow[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = pr + 64 * i;
+        arow[i] = -1;
+        if (m0 + r < rows) {
+            const int p = row_lo + m0 + r;
+            arow[i] = a.row_src ? a.row_src[p] : p;
+        }
+    }
+    const bool wok = n0 + pr < a.N;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    uint4 ra[2], rw[2];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            ra[i] = arow[i] >= 0 ? *reinterpret_cast<const uint4*>(A + arow[i] * a.lda + k0 + pc) : zero;
+        rw[0] = wok ? *reinterpret_cast<const uint4*>(W + (int64_t)(n0 + pr) * a.ldw + k0 + pc) : zero;
+        if (DUAL) rw[1] = wok ? *reinterpret_cast<const uint4*>(W + (int64_t)(a.N + n0 + pr) * a.ldw + k0 + pc) : zero;
+    };
+    auto stash = [&](int s) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) *reinterpret_cast<uint4*>(&As[s][pr + 64 * i][pc]) = ra[i];
+        *reinterpret_cast<uint4*>(&Ws[s][0][pr][pc]) = rw[0];
+        if (DUAL) *reinterpret_cast<uint4*>(&Ws[s][DUAL ? 1 : 0][pr][pc]) = rw[1];
+    };
+    float acc[2][4][4] = {}, acc2[DUAL ? 2 : 1][4][4] = {};
+    const int nk = a.K / TK;           // the host routes K % 32 != 0 to the SIMT kernel
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    const int gr = lane >> 2, gc = (lane & 3) * 2;
+    for (int kt = 0; kt < nk; ++kt) {
+        const int s = kt & 1;
+        if (kt + 1 < nk) fetch((kt + 1) * TK);
+#pragma unroll
+        for (int kk = 0; kk < TK; kk += 16) {
+            uint32_t af[2][4], bf[4][2], bf2[4][2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = wm + 16 * i + gr;
+                af[i][0] = *reinterpret_cast<const uint32_t*>(&As[s][r][kk + gc]);
+                af[i][1] = *reinterpret_cast<const uint32_t*>(&As[s][r + 8][kk + gc]);
+                af[i][2] = *reinterpret_cast<const uint32_t*>(&As[s][r][kk + gc + 8]);
+                af[i][3] = *reinterpret_cast<const uint32_t*>(&As[s][r + 8][kk + gc + 8]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = wn + 8 * j + gr;
+                bf[j][0] = *reinterpret_cast<const uint32_t*>(&Ws[s][0][n][kk + gc]);
+                bf[j][1] = *reinterpret_cast<const uint32_t*>(&Ws[s][0][n][kk + gc + 8]);
+                if (DUAL) {
+                    bf2[j][0] = *reinterpret_cast<const uint32_t*>(&Ws[s][DUAL ? 1 : 0][n][kk + gc]);
+                    bf2[j][1] = *reinterpret_cast<const uint32_t*>(&Ws[s][DUAL ? 1 : 0][n][kk + gc + 8]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    mma_bf16(acc[i][j], af[i], bf[j]);
+                    if (DUAL) mma_bf16(acc2[DUAL ? i : 0][j], af[i], bf2[j]);
+                }
+        }
+        if (kt + 1 < nk) {
+            stash(s ^ 1);            // the other stage was last read before the barrier that ended step kt - 1
+            __syncthreads();
+        }
+    }
+    TC* C = (TC*)a.C + (int64_t)g * a.c_goff;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int m = m0 + wm + 16 * i + gr + (e >> 1) * 8, n = n0 + wn + 8 * j + gc + (e & 1);
+                if (m >= rows || n >= a.N) continue;
+                const float v = DUAL ? gated_act(acc[i][j][e], acc2[DUAL ? i : 0][j][e], a.limit) : acc[i][j][e];
+                C[(int64_t)(row_lo + m) * a.ldc + n] = from_f32<TC>(v);
+            }
+}
+
+template <typename TA, typename TC>
+static void launch_simt(const GemmArgs& a, int groups, bool dual, cudaStream_t st) {
+    const dim3 grid((a.N + BN - 1) / BN, (a.M + BM - 1) / BM, groups);
+    if (dual) gemm_simt_kernel<TA, TC, true><<<grid, 256, 0, st>>>(a);
+    else gemm_simt_kernel<TA, TC, false><<<grid, 256, 0, st>>>(a);
+}
+template <typename TC>
+static void launch_mma(const GemmArgs& a, int groups, bool dual, cudaStream_t st) {
+    const dim3 grid((a.N + TN - 1) / TN, (a.M + TM - 1) / TM, groups);
+    if (dual) gemm_mma_kernel<TC, true><<<grid, 256, 0, st>>>(a);
+    else gemm_mma_kernel<TC, false><<<grid, 256, 0, st>>>(a);
+}
+
+}  // namespace umbs
+
+using namespace umbs;
+
+extern "C" int umbs_gemm(int dtype, const void* A, int64_t lda, int a_goff, const void* W, int64_t ldw, int64_t w_gstride,
+                         void* C, int64_t ldc, int c_goff, int c_f32, int M, int N, int K, int groups,
+                         const int32_t* grp_off, const int32_t* row_src, int dual, float limit, umbs_stream_t stream) {
+    if (M <= 0 || N <= 0 || groups <= 0) return 0;
+    if (K <= 0 || A == nullptr || W == nullptr || C == nullptr) return UMB_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    GemmArgs a{A, lda, a_goff, W, ldw, w_gstride, C, ldc, c_goff, M, N, K, grp_off, row_src, limit};
+    if (dtype == UMBS_F32) {
+        launch_simt<float, float>(a, groups, dual != 0, st);          // activations are fp32 too: c_f32 changes nothing
+    } else if (dtype == UMBS_BF16) {
+        // 16-byte loads: every row start and group offset must sit on a 16-byte boundary
+        const bool tc = (K % TK == 0) && (lda % 8 == 0) && (ldw % 8 == 0) && (a_goff % 8 == 0) && (w_gstride % 8 == 0) &&
+                        ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0);
+        if (tc) {
+            if (c_f32) launch_mma<float>(a, groups, dual != 0, st);
+            else launch_mma<__nv_bfloat16>(a, groups, dual != 0, st);
+        } else {
+            if (c_f32) launch_simt<__nv_bfloat16, float>(a, groups, dual != 0, st);
+            else launch_simt<__nv_bfloat16, __nv_bfloat16>(a, groups, dual != 0, st);
+        }
+    } else {
+        return UMB_ERR_ARG;
+    }
+    count_launches(1);
+    return (int)cudaGetLastError();
+}

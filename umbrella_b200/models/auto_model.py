@@ -32,7 +32,36 @@ def _weight_bytes(shape, awq: bool) -> int:
     return int(body + head)
 
 
-def _make(model_name, offload=False, batch_size=1, max_length=256, device="cuda:0", dtype=torch.float16, **unused):
+def _architecture_of(model_name) -> str | None:
+    """The ``architecture`` key of a checkpoint directory's config.json (families other than Llama name themselves there)."""
+    f = os.path.join(str(model_name), "config.json")
+    if not os.path.isfile(f):
+        return None
+    try:
+        import json
+        return json.load(open(f)).get("architecture")
+    except (OSError, ValueError):
+        return None
+
+
+def _radanex(path, **kw):
+    from . import radanex
+    return radanex.from_pretrained(path, **kw)
+
+
+# config.json ``architecture`` -> factory(path, device=, dtype=, max_length=, slots=, max_tokens=)
+_ARCHITECTURES = {"Radanex": _radanex}
+
+
+def _make(model_name, offload=False, batch_size=1, max_length=None, device="cuda:0", dtype=torch.float16, **unused):
+    arch = _architecture_of(model_name)
+    if arch in _ARCHITECTURES:
+        if offload:
+            raise ValueError(f"{arch}: weight offloading is not implemented for sequence-state decoders")
+        kw = {k: unused[k] for k in ("slots", "max_tokens") if k in unused}
+        return _ARCHITECTURES[arch](str(model_name), device=device, dtype=torch.bfloat16 if dtype == torch.float16 else dtype,
+                                    max_length=max_length, **kw)
+    max_length = 256 if max_length is None else max_length          # the reference's default (models/base.py)
     entry = L.KNOWN_MODELS.get(model_name)
     if entry is None and os.path.isfile(os.path.join(str(model_name), "config.json")):
         from .checkpoint import shape_from_config

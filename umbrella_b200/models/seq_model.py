@@ -1,0 +1,275 @@
+"""Sequence-state decoders on the native batched step (umbs_forward of libumbrella_b200_seq.so).
+
+A model is a ``SeqModelSpec``: width, vocabulary, the grouped RMS norm's constants and a list of ``SeqLayerSpec``s,
+each naming its mixer (``"retention"`` or ``"latent_attention"``) with that mixer's sizes and constants, whether it
+has token shift and a depth average, and its feed-forward (routed experts and / or a shared expert, or none).  Model
+families (models/radanex.py) translate their config.json into a spec and their tensors into the per-layer weight
+dicts ``load_layer`` takes; nothing below knows a family's names.
+
+One ``forward`` call runs a ragged batch: for every sequence its slot of the ``SequenceStateCache`` and its next
+tokens (any number: a whole prompt, a portion of one, one decoded token), and the places whose logits are wanted.
+The batch description goes host -> device in one pinned copy; one C call enqueues every launch of the step.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+
+import torch
+
+from .. import _lib_seq as S
+from ..attn.state_cache import SequenceStateCache
+
+
+@dataclass
+class SeqMlpSpec:
+    experts: int = 0
+    top: int = 0
+    ff: int = 0
+    limit: float = 0.0
+    shared_ff: int = 0
+    shared_limit: float = 0.0
+
+
+@dataclass
+class SeqLayerSpec:
+    mixer: str = "retention"
+    heads: int = 1
+    dim: int = 32
+    vdim: int = 32
+    # retention
+    rot_dims: int = 0
+    rot_base: float = 10000.0
+    decay: list = field(default_factory=list)
+    # latent attention
+    q_rank: int = 0
+    kv_rank: int = 0
+    window: int = 0
+    scale: float = 1.0
+    # layer
+    shift: bool = True
+    depth_average: bool = True
+    mlp: SeqMlpSpec | None = None
+
+
+@dataclass
+class SeqModelSpec:
+    width: int
+    vocab: int
+    layers: list
+    norm_groups: int = 1
+    norm_eps: float = 1e-6
+    eos_token_id: list = field(default_factory=list)
+
+    # compatibility with the engines' view of a config
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @property
+    def num_hidden_layers(self) -> int:
+        return len(self.layers)
+
+
+def rotary_inv_freq(rot_dims: int, base: float) -> torch.Tensor:
+    """f_i = base^(-2 i / rot_dims), i < rot_dims / 2: evaluated in double, rounded once to fp32."""
+    i = torch.arange(rot_dims // 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / rot_dims).to(torch.float32)
+
+
+class SeqStateModel:
+    """Weights + state cache + workspace of one sequence-state decoder on one GPU."""
+
+    def __init__(self, spec: SeqModelSpec, device="cuda:0", dtype=torch.bfloat16, slots: int = 8,
+                 max_length: int | None = None, max_tokens: int = 0, model_name: str | None = None):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise TypeError("sequence-state decoders run in bfloat16 or float32")
+        self.spec = self.config = spec
+        self.device, self.dtype = torch.device(device), dtype
+        self.model_name = model_name
+        self.max_length = max_length
+        self.num_layers = len(spec.layers)
+        self.eos_tokens = list(spec.eos_token_id)
+        self._slots0, self._max_tokens0 = slots, max_tokens
+        self.weights: list[dict | None] = [None] * self.num_layers
+        self.head_weights: dict | None = None
+        self.cache: SequenceStateCache | None = None
+        self._c_model = None
+        self._c_version = -1
+        self._ws = None
+        self._ws_tokens = self._ws_want = 0
+        self._pinned = None
+        self._dev_ints = None
+
+    # ------------------------------------------------------------------ allocation
+    def alloc(self, **kwargs):
+        S.load()
+        if self.device.type != "cuda":
+            raise RuntimeError("sequence-state decoders need a CUDA device (there is no CPU path)")
+        self.cache = SequenceStateCache(self.spec, slots=kwargs.get("slots", self._slots0), device=self.device,
+                                        dtype=self.dtype, max_length=self.max_length)
+        return self
+
+    def _reserve(self, tokens: int, want: int):
+        if self._ws is not None and tokens <= self._ws_tokens and want <= self._ws_want:
+            return
+        tokens, want = max(tokens, self._ws_tokens), max(want, self._ws_want)
+        n = S.load().umbs_workspace_bytes(C.byref(self._model_struct()), tokens, want)
+        self._ws = None
+        self._ws = torch.empty(n, dtype=torch.uint8, device=self.device)
+        self._ws_tokens, self._ws_want = tokens, want
+
+    # ------------------------------------------------------------------ weights
+    def _act(self, t: torch.Tensor) -> torch.Tensor:
+        return t.to(self.device, self.dtype).contiguous()
+
+    def _f32(self, t: torch.Tensor) -> torch.Tensor:
+        return t.to(self.device, torch.float32).contiguous()
+
+    def load_head(self, embed: torch.Tensor, head: torch.Tensor, final_norm: torch.Tensor):
+        self.head_weights = dict(embed=self._act(embed), head=self._act(head), final_norm=self._f32(final_norm))
+        self._c_model = None
+
+    def load_layer(self, idx: int, w: dict):
+        """``w``: tensors [out, in] as the checkpoint holds them.
+        all layers: norm [width]; shift [width] (if the layer shifts); depth [idx + 2] (if it averages); o.
+        retention: q, k [heads dim, width]; v, g [heads vdim, width].
+        latent attention: dq [q_rank, width], dq_norm, uq [heads dim, q_rank], dkv [kv_rank, width], dkv_norm,
+            uk [heads dim, kv_rank], uv [heads vdim, kv_rank].
+        feed-forward: router [experts, width]; experts: list of (gate, up, down); shared: (gate, up, down)."""
+        l = self.spec.layers[idx]
+        d = dict(norm=self._f32(w["norm"]), o=self._act(w["o"]))
+        if l.shift:
+            d["shift"] = self._f32(w["shift"])
+        if l.depth_average:
+            d["depth"] = self._f32(w["depth"])
+            assert d["depth"].numel() == idx + 2
+        if l.mixer == "retention":
+            d["w_in"] = self._act(torch.cat([w["q"], w["k"], w["v"], w["g"]], dim=0))
+            d["inv_freq"] = rotary_inv_freq(l.rot_dims, l.rot_base).to(self.device) if l.rot_dims else \
+                torch.zeros(1, dtype=torch.float32, device=self.device)
+            d["decay"] = torch.tensor([float(x) for x in l.decay], dtype=torch.float32, device=self.device)
+            assert d["decay"].numel() == l.heads and d["w_in"].shape == (2 * l.heads * (l.dim + l.vdim), self.spec.width)
+        elif l.mixer == "latent_attention":
+            d["w_in"] = self._act(torch.cat([w["dq"], w["dkv"]], dim=0))
+            d["q_norm"], d["kv_norm"] = self._f32(w["dq_norm"]), self._f32(w["dkv_norm"])
+            d["uq"] = self._act(w["uq"])
+            # key up-projection transposed per head: [heads, dim, kv_rank] -> [heads, kv_rank, dim]
+            d["ukT"] = self._act(w["uk"].reshape(l.heads, l.dim, l.kv_rank).transpose(1, 2))
+            d["uv"] = self._act(w["uv"])
+            assert d["uq"].shape == (l.heads * l.dim, l.q_rank) and d["uv"].shape == (l.heads * l.vdim, l.kv_rank)
+        else:
+            raise ValueError(f"unknown mixer '{l.mixer}'")
+        assert d["o"].shape == (self.spec.width, l.heads * l.vdim)
+        if l.mlp is not None:
+            m = l.mlp
+            if m.experts:
+                d["router"] = self._f32(w["router"])
+                d["gu"] = self._act(torch.stack([torch.cat([g, u], dim=0) for g, u, _ in w["experts"]]))
+                d["down"] = self._act(torch.stack([dn for _, _, dn in w["experts"]]))
+                assert d["gu"].shape == (m.experts, 2 * m.ff, self.spec.width)
+            if m.shared_ff:
+                g, u, dn = w["shared"]
+                d["s_gu"], d["s_down"] = self._act(torch.cat([g, u], dim=0)), self._act(dn)
+                assert d["s_gu"].shape == (2 * m.shared_ff, self.spec.width)
+        self.weights[idx] = d
+        self._c_model = None
+
+    def weight_bytes(self) -> int:
+        n = sum(t.numel() * t.element_size() for t in self.head_weights.values())
+        for d in self.weights:
+            n += sum(t.numel() * t.element_size() for t in d.values())
+        return n
+
+    # ------------------------------------------------------------------ C structs
+    def _model_struct(self) -> S.Model:
+        if self._c_model is not None and self._c_version == self.cache.version:
+            return self._c_model
+        assert self.head_weights is not None and all(w is not None for w in self.weights), "load every layer first"
+        sp, cache = self.spec, self.cache
+        p = lambda t: t.data_ptr() if t is not None else None
+        layers = (S.Layer * self.num_layers)()
+        for i, (l, w) in enumerate(zip(sp.layers, self.weights)):
+            cl = layers[i]
+            cl.mixer = S.UMBS_MIX_RETENTION if l.mixer == "retention" else S.UMBS_MIX_LATENT_ATTENTION
+            cl.heads, cl.dim, cl.vdim = l.heads, l.dim, l.vdim
+            if l.mixer == "retention":
+                cl.rot_dims, cl.inv_freq, cl.decay = l.rot_dims, p(w["inv_freq"]), p(w["decay"])
+                cl.ret_state = p(cache.ret_state[i])
+            else:
+                cl.q_rank, cl.kv_rank, cl.window, cl.ring_len = l.q_rank, l.kv_rank, l.window, cache.ring_len(l)
+                cl.scale = l.scale
+                cl.q_norm, cl.kv_norm, cl.w_uq, cl.w_ukT, cl.w_uv = p(w["q_norm"]), p(w["kv_norm"]), p(w["uq"]), \
+                    p(w["ukT"]), p(w["uv"])
+                cl.ring = p(cache.ring[i])
+            cl.w_in, cl.w_o, cl.norm_w = p(w["w_in"]), p(w["o"]), p(w["norm"])
+            cl.shift_w, cl.shift_state = p(w.get("shift")), p(cache.shift[i])
+            cl.depth_w = p(w.get("depth"))
+            cl.has_mlp = int(l.mlp is not None)
+            if l.mlp is not None:
+                m = l.mlp
+                cl.mlp.experts, cl.mlp.top, cl.mlp.ff, cl.mlp.limit = m.experts, m.top, m.ff, m.limit
+                cl.mlp.w_router, cl.mlp.w_gu, cl.mlp.w_down = p(w.get("router")), p(w.get("gu")), p(w.get("down"))
+                cl.mlp.shared_ff, cl.mlp.shared_limit = m.shared_ff, m.shared_limit
+                cl.mlp.ws_gu, cl.mlp.ws_down = p(w.get("s_gu")), p(w.get("s_down"))
+        m = S.Model()
+        m.dtype = S.UMBS_BF16 if self.dtype == torch.bfloat16 else S.UMBS_F32
+        m.width, m.vocab, m.n_layers, m.norm_groups, m.slots = sp.width, sp.vocab, self.num_layers, sp.norm_groups, cache.slots
+        m.norm_eps = sp.norm_eps
+        hw = self.head_weights
+        m.embed, m.final_norm, m.head = p(hw["embed"]), p(hw["final_norm"]), p(hw["head"])
+        m.layers = C.cast(layers, C.POINTER(S.Layer))
+        self._c_layers = layers
+        self._c_model, self._c_version = m, self.cache.version
+        return m
+
+    # ------------------------------------------------------------------ the step
+    @torch.inference_mode()
+    def forward(self, entries, layer_out: bool = False):
+        """``entries``: [(slot, tokens, want)], the next tokens of every sequence of the step and the indices among
+        them whose logits are wanted.  Returns fp32 logits [sum of wants, vocab] in entry order (and, with
+        ``layer_out``, the residual stream after every layer, [layers, tokens, width]).  The slots' positions advance."""
+        cache = self.cache
+        ids, tok_seq, tok_pos, want = [], [], [], []
+        slot, start, length, pos0, parity = [], [], [], [], []
+        for b, (s, toks, w) in enumerate(entries):
+            n = len(toks)
+            if n == 0:
+                raise ValueError("an entry without tokens")
+            p0 = cache.position[s]
+            if self.max_length is not None and p0 + n > self.max_length:
+                raise RuntimeError(f"sequence longer than max_length {self.max_length}")
+            slot.append(s), start.append(len(ids)), length.append(n), pos0.append(p0), parity.append(cache.parity[s])
+            want += [len(ids) + int(i) for i in w]
+            ids += [int(t) for t in toks]
+            tok_seq += [b] * n
+            tok_pos += range(p0, p0 + n)
+        T, B, Wn = len(ids), len(entries), len(want)
+        if T == 0:
+            return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=self.device)
+        if len(set(slot)) != B:
+            raise ValueError("a slot appears twice in one step")
+        flat = ids + tok_seq + tok_pos + slot + start + length + pos0 + parity + want
+        host = torch.tensor(flat, dtype=torch.int32).pin_memory()
+        dev = host.to(self.device, non_blocking=True)
+        self._reserve(max(T, self._max_tokens0), max(Wn, 1))       # sized once for the largest step announced
+        base, o = dev.data_ptr(), 0
+        bt = S.Batch()
+        bt.n_tokens, bt.n_seqs, bt.n_want, bt.max_seq_len = T, B, Wn, max(length)
+        for name, n in (("tok_ids", T), ("tok_seq", T), ("tok_pos", T), ("seq_slot", B), ("seq_start", B), ("seq_len", B),
+                        ("seq_pos0", B), ("seq_parity", B), ("want_rows", Wn)):
+            setattr(bt, name, base + 4 * o)
+            o += n
+        logits = torch.empty((Wn, self.spec.vocab), dtype=torch.float32, device=self.device)
+        layers = torch.empty((self.num_layers, T, self.spec.width), dtype=torch.float32, device=self.device) \
+            if layer_out else None
+        S.check(S.load().umbs_forward(C.byref(self._model_struct()), C.byref(bt), logits.data_ptr() if Wn else None,
+                                      layers.data_ptr() if layer_out else None, self._ws.data_ptr(), self._ws.numel(),
+                                      torch.cuda.current_stream().cuda_stream), "forward")
+        self._keep = (host, dev)              # alive until the next step is enqueued behind this one
+        for s, n in zip(slot, length):
+            cache.advance(s, n)
+        return (logits, layers) if layer_out else logits
+
+    def clear(self):
+        self.cache.clear()

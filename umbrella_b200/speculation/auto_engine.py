@@ -12,7 +12,10 @@ from importlib import import_module
 _REGISTRY = {
     "static": ("static_speculation_engine", "StaticSpeculationEngine"),
     "dynamic": ("dynamic_speculation_engine", "DynamicSpeculationEngine"),
+    # plain batched decoding for sequence-state models (no draft model: a recurrent state cannot roll back a tree)
+    "batch": ("batch_engine", "BatchDecodingEngine"),
 }
+_NO_DRAFT = ("batch",)
 # keys of configs/*.json that belong to the chat / API front-ends, not to an engine (app/chatbot.py:17-19)
 _FRONT_END_KEYS = ("generation_length", "max_turns", "template")
 
@@ -27,11 +30,12 @@ def engine_class(name: str):
 class AutoEngine:
     @staticmethod
     def from_config(device: str, **config):
-        cls = engine_class(config.pop("engine", "dynamic"))
+        engine = config.pop("engine", "dynamic")
+        cls = engine_class(engine)
         names = {role: config.pop(key, None) for role, key in (("draft_model_name", "draft_model"),
                                                                 ("target_model_name", "model"))}
         for role, value in names.items():
-            assert value is not None, f"config lacks the {role.replace('_name', '').replace('_', ' ')}"
+            assert value is not None or (engine in _NO_DRAFT and role == "draft_model_name"), f"config lacks the {role.replace('_name', '').replace('_', ' ')}"
         for key in _FRONT_END_KEYS:
             config.pop(key, None)
         return cls(device=device, **names, **config)
