@@ -1,0 +1,111 @@
+"""Host-side logic of the sequence-state decoders that needs no GPU: the family's config reader, the slot
+bookkeeping of the state cache, the batch engine's queue, and the C ABI table against its header."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+import seq_helpers as H
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_config_reader_maps_every_key():
+    from umbrella_b200.models.radanex import layer_tensor_names, spec_from_config
+    spec = spec_from_config(H.config_json(H.MIXED))
+    assert (spec.width, spec.vocab, spec.norm_groups, spec.norm_eps) == (64, 96, 2, 1e-5)
+    lat, ret = spec.layers[0], spec.layers[1]
+    assert (lat.mixer, lat.heads, lat.dim, lat.vdim, lat.q_rank, lat.kv_rank, lat.window, lat.scale) == \
+        ("latent_attention", 2, 16, 24, 40, 48, 9, 0.3)
+    assert (ret.mixer, ret.rot_dims, ret.rot_base, ret.decay) == ("retention", 8, 100.0, [0.9, 0.97, 0.9990234375])
+    assert spec.layers[2].mlp is None and spec.layers[1].mlp.shared_ff == 0
+    assert spec.layers[4].mlp.experts == 0 and spec.layers[4].mlp.shared_ff == 24 and spec.layers[3].mlp.top == 1
+    names = layer_tensor_names(spec, 3)
+    assert names["experts"][2] == ("l3.mlp.e2.gate", "l3.mlp.e2.up", "l3.mlp.e2.down") and names["depth"] == "l3.dwa"
+    assert set(n for i in range(5) for v in layer_tensor_names(spec, i).values()
+               for n in ([v] if isinstance(v, str) else [x for y in v for x in ([y] if isinstance(y, str) else y)])) \
+        | {"embed", "head", "final.norm"} == set(H.random_tensors(H.MIXED))
+    with pytest.raises(ValueError):
+        spec_from_config(dict(H.config_json(H.MIXED), architecture="Other"))
+
+
+def test_auto_model_picks_the_family_from_config_json(tmp_path):
+    from umbrella_b200.models.auto_model import AutoModelLM
+    from umbrella_b200.models.radanex import Radanex
+    path = H.write_checkpoint(str(tmp_path / "m"), H.ALIGNED, H.random_tensors(H.ALIGNED))
+    m = AutoModelLM.from_pretrained(path, device="cuda:0", dtype=torch.float32)
+    assert isinstance(m, Radanex) and m.num_layers == 2 and m.dtype == torch.float32
+
+
+def test_state_cache_slots():
+    from umbrella_b200.attn.state_cache import SequenceStateCache
+    from umbrella_b200.models.radanex import spec_from_config
+    spec = spec_from_config(H.config_json(H.MIXED))
+    c = SequenceStateCache(spec, slots=2, device="cpu", dtype=torch.float32, max_length=20)
+    assert c.ring[0].shape == (2, 9, 48) and c.ring[2].shape == (2, 20, 48)        # window 33 capped by max_length
+    assert c.ret_state[1].shape == (2, 3, 16, 32) and c.shift[4].shape == (2, 2, 64) and c.ring[1] is None
+    a, b = c.alloc_slot(), c.alloc_slot()
+    c.ret_state[1][b].fill_(3.0)
+    c.advance(b, 5)
+    assert (c.position[b], c.parity[b]) == (5, 1)
+    d = c.alloc_slot()                                               # full: the cache doubles and keeps its contents
+    assert c.slots == 4 and d == 2 and float(c.ret_state[1][b].min()) == 3.0 and c.position[b] == 5
+    c.free_slot(b)
+    with pytest.raises(ValueError):
+        c.free_slot(b)
+    assert c.live_slots == 2
+    e = c.alloc_slot()
+    assert e == 3 and c.alloc_slot() == b and c.position[b] == 0 and c.parity[b] == 0       # freed slots go to the back
+
+
+class _FakeModel:
+    """Counts the steps; the 'logits' make token (last input + 1) the arg-max."""
+    eos_tokens = [7]
+    device = "cpu"
+
+    def __init__(self):
+        from umbrella_b200.attn.state_cache import SequenceStateCache
+        from umbrella_b200.models.radanex import spec_from_config
+        self.cache = SequenceStateCache(spec_from_config(H.config_json(H.ALIGNED)), slots=2, device="cpu", dtype=torch.float32)
+        self.steps = []
+
+    def forward(self, entries):
+        self.steps.append([(s, len(t)) for s, t, _ in entries])
+        rows = []
+        for s, t, w in entries:
+            self.cache.advance(s, len(t))
+            for i in w:
+                row = torch.zeros(16)
+                row[(t[i] + 1) % 16] = 1.0
+                rows.append(row)
+        return torch.stack(rows)
+
+
+def test_batch_engine_queue_and_slots():
+    from umbrella_b200.speculation.auto_engine import AutoEngine
+    eng = AutoEngine.from_config("cpu", engine="batch", model="unused", max_batch=2, max_tokens=10)
+    fake = _FakeModel()
+    eng.initialize(model=fake)
+    eng.sample = lambda logits: logits.argmax(-1)
+    outs = eng.generate_batch([[1, 2, 3], [4, 5], [9, 9, 9, 9, 9, 9, 9, 9, 9], [0]], max_new_tokens=4)
+    assert outs == [[4, 5, 6, 7], [6, 7], [10, 11, 12, 13], [1, 2, 3, 4]]           # 7 is EOS: request 1 leaves early
+    assert fake.steps[0] == [(0, 3), (1, 2)]                   # first batch: two requests, prompts in one ragged step
+    assert fake.steps[1] == [(0, 1), (1, 1)] and fake.steps[2] == [(0, 1)]          # the shorter one has left
+    # second batch: the 9-token prompt alone would fit with the 1-token one only under max_tokens = 10
+    assert [len(s) for s in fake.steps[4:6]] == [2, 2] and fake.cache.live_slots == 0
+    with pytest.raises(ValueError):
+        AutoEngine.from_config("cpu", engine="nope", model="m")
+
+
+def test_seq_abi_table_matches_header_and_library():
+    from umbrella_b200 import _lib_seq, build
+    text = open(os.path.join(ROOT, "include", "umbrella_b200_seq.h")).read()
+    declared = sorted(set(re.findall(r"\b(umbs_[a-z0-9_]+)\s*\(", text)))
+    assert declared == sorted(_lib_seq.SIGNATURES)
+    lib = ctypes.CDLL(build.build_seq())                              # nvcc cross-compiles without a GPU
+    for n in declared:
+        assert hasattr(lib, n), n
+    lib.umbs_version.restype = ctypes.c_char_p
+    assert lib.umbs_version().startswith(b"umbrella_b200_seq")

@@ -1,0 +1,138 @@
+"""Tensor-level wrappers over the building blocks of libumbrella_b200_seq.so (torch tensors in, raw pointers out),
+the counterpart of ops.py for the sequence-state decoders.  Each call enqueues on ``torch.cuda.current_stream()``.
+
+``dtype`` of the activations / weights is read off the tensors: torch.bfloat16 or torch.float32.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib_seq as S
+
+
+def _p(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _mode(t: torch.Tensor) -> int:
+    if not t.is_cuda:
+        raise RuntimeError("CUDA tensors only (there is no CPU path)")
+    if t.dtype == torch.bfloat16:
+        return S.UMBS_BF16
+    if t.dtype == torch.float32:
+        return S.UMBS_F32
+    raise TypeError(f"bfloat16 or float32 expected, got {t.dtype}")
+
+
+def _i32(x, device):
+    return torch.as_tensor(x, dtype=torch.int32).to(device)
+
+
+class RaggedBatch:
+    """Device copy of one step's batch description.  ``seqs``: [(slot, n_tokens, pos0, parity)]."""
+
+    def __init__(self, seqs, device, token_ids=None, want=None):
+        tok_seq, tok_pos, start = [], [], []
+        for b, (slot, n, pos0, par) in enumerate(seqs):
+            start.append(len(tok_seq))
+            tok_seq += [b] * n
+            tok_pos += range(pos0, pos0 + n)
+        T = len(tok_seq)
+        self.t = dict(tok_ids=_i32(token_ids if token_ids is not None else [0] * T, device), tok_seq=_i32(tok_seq, device),
+                      tok_pos=_i32(tok_pos, device), seq_slot=_i32([s[0] for s in seqs], device),
+                      seq_start=_i32(start, device), seq_len=_i32([s[1] for s in seqs], device),
+                      seq_pos0=_i32([s[2] for s in seqs], device), seq_parity=_i32([s[3] for s in seqs], device),
+                      want_rows=_i32(want if want is not None else [], device))
+        c = S.Batch()
+        c.n_tokens, c.n_seqs, c.n_want = T, len(seqs), len(want) if want is not None else 0
+        c.max_seq_len = max(s[1] for s in seqs) if seqs else 0
+        for k, v in self.t.items():
+            setattr(c, k, v.data_ptr())
+        self.c, self.n_tokens = c, T
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, *, out_f32: bool = False, groups: int = 1, a_goff: int = 0, c_goff: int = 0,
+         n: int | None = None, k: int | None = None, grp_off=None, row_src=None, rows: int | None = None,
+         dual: bool = False, limit: float = 0.0, max_rows: int | None = None) -> torch.Tensor:
+    """a [M, lda] x w ([groups,] N(or 2N if dual), K) -> [rows, groups * c_goff or N].  See umbs_gemm."""
+    mode = _mode(a)
+    assert w.dtype == a.dtype and a.stride(-1) == 1 and w.is_contiguous()
+    w3 = w if w.dim() == 3 else w.unsqueeze(0)
+    K = w3.shape[2] if k is None else k
+    N = (w3.shape[1] // (2 if dual else 1)) if n is None else n
+    M = a.shape[0] if rows is None else rows
+    cols = N if (groups == 1 or grp_off is not None) else groups * c_goff        # expert groups share the columns
+    out = torch.zeros((M, cols), dtype=torch.float32 if out_f32 else a.dtype, device=a.device)
+    S.check(S.load().umbs_gemm(mode, _p(a), a.stride(0), a_goff, _p(w3), w3.stride(1), w3.stride(0), _p(out), out.stride(0),
+                               c_goff, int(out_f32), M if max_rows is None else max_rows, N, K, groups, _p(grp_off),
+                               _p(row_src), int(dual), float(limit), _stream()), "gemm")
+    return out
+
+
+def group_norm_shift(x, w, shift_w, shift_state, batch: RaggedBatch, groups: int, eps: float, dtype=torch.float32):
+    T, width = x.shape
+    h = torch.empty((T, width), dtype=dtype, device=x.device)
+    hs = torch.empty_like(h)
+    S.check(S.load().umbs_group_norm_shift(_mode(h), _p(x), _p(w), _p(shift_w), _p(shift_state), shift_state.shape[1],
+                                           C.byref(batch.c), width, groups, float(eps), _p(h), _p(hs), _stream()),
+            "group_norm_shift")
+    return h, hs
+
+
+def retention(qkvg, batch: RaggedBatch, heads, dim, vdim, rot_dims, inv_freq, decay, eps, state, dtype=torch.float32):
+    T = qkvg.shape[0]
+    o32 = torch.empty((T, heads * vdim), dtype=torch.float32, device=qkvg.device)
+    out = torch.empty((T, heads * vdim), dtype=dtype, device=qkvg.device)
+    S.check(S.load().umbs_retention(_mode(out), _p(qkvg), qkvg.stride(0), C.byref(batch.c), heads, dim, vdim, rot_dims,
+                                    _p(inv_freq), _p(decay), float(eps), _p(state), _p(o32), _p(out), _stream()), "retention")
+    return out
+
+
+def latent_attention(q_abs, c, ring, batch: RaggedBatch, heads, window, scale, append: bool = True):
+    T, R = c.shape
+    out = torch.empty((T, heads * R), dtype=c.dtype, device=c.device)
+    lib = S.load()
+    S.check(lib.umbs_latent_attention(_mode(c), _p(q_abs), _p(c), _p(ring), ring.shape[1], C.byref(batch.c), heads, R, window,
+                                      float(scale), _p(out), _stream()), "latent_attention")
+    if append:
+        S.check(lib.umbs_ring_append(_mode(c), _p(c), _p(ring), ring.shape[1], C.byref(batch.c), R, _stream()), "ring_append")
+    return out
+
+
+def latent_norm(x, q_rank, kv_rank, q_norm, kv_norm, eps, dtype=torch.float32):
+    n = x.shape[0]
+    cq = torch.empty((n, q_rank), dtype=dtype, device=x.device)
+    c = torch.empty((n, kv_rank), dtype=dtype, device=x.device)
+    S.check(S.load().umbs_latent_norm(_mode(c), _p(x), n, q_rank, kv_rank, _p(q_norm), _p(kv_norm), float(eps), _p(cq), _p(c),
+                                      _stream()), "latent_norm")
+    return cq, c
+
+
+def moe_route(h, w_router, top: int):
+    """-> (sel_w [n, top] fp32, grp_off [E + 1], pair_tok [n top], pair_pos [n top], sel_e [n top])."""
+    n, width = h.shape
+    E = w_router.shape[0]
+    dev = h.device
+    sel_w = torch.empty((n, top), dtype=torch.float32, device=dev)
+    grp_off = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    pair_tok = torch.empty(n * top, dtype=torch.int32, device=dev)
+    pair_pos = torch.empty(n * top, dtype=torch.int32, device=dev)
+    scratch = torch.empty(2 * E + n * top, dtype=torch.int32, device=dev)
+    S.check(S.load().umbs_moe_route(_mode(h), _p(h), n, width, _p(w_router), E, top, _p(sel_w), _p(grp_off), _p(pair_tok),
+                                    _p(pair_pos), _p(scratch), _stream()), "moe_route")
+    return sel_w, grp_off, pair_tok, pair_pos, scratch[2 * E:].view(n, top)
+
+
+def depth_mix(x, mix, stack, layer: int, depth_w, pair_out=None, sel_w=None, pair_pos=None, shared=None):
+    n, width = x.shape
+    out = torch.empty_like(x)
+    top = sel_w.shape[1] if sel_w is not None else 0
+    S.check(S.load().umbs_depth_mix(_p(x), _p(mix), _p(pair_out), _p(sel_w), _p(pair_pos), top, _p(shared), _p(stack), layer,
+                                    _p(depth_w), _p(out), None, n, width, _stream()), "depth_mix")
+    return out
