@@ -14,6 +14,7 @@ scripted acceptance with the reference's DEFAULT_ACC (random weights make draft 
   stochastic32k  (configs[3]) 70B-AWQ + 1B, T = 0.6 / top-p 0.9 / top-k 32 / repetition penalty 1.05 (chat_config_48gb),
                  prompt 30000, max_length 32768, KV pages of the upper layers resident in pinned host memory
   stochastic32k_hbm  the same with the whole KV cache in HBM
+  radanex            the sequence-state decoder family next to Llama at equal size (prefill / decode tokens/s, kernel table)
   static70b_b200tree the default workload on the packaged B200-tuned 16-node tree (sequoia_utils.generate_budget_tree)
 
 A *step* is one speculative-decoding iteration (draft build_tree + target verify + accept + KV gather).  ``value`` =
@@ -66,6 +67,8 @@ WORKLOADS["static70b_b200tree"] = dict(WORKLOADS["static70b"], tree="b200_sequoi
 WORKLOADS["stochastic32k_hbm"] = dict(WORKLOADS["stochastic32k"], kv_host_layers=0,
                                       text=WORKLOADS["stochastic32k"]["text"].replace(
                                           "KV pages of layers 40..79 in pinned host memory", "KV cache resident in HBM"))
+# the sequence-state decoder family beside Llama at equal size: its own report (umbrella_b200/seq_bench.py), not the headline
+WORKLOADS["radanex"] = dict(text="Radanex bf16 vs Llama fp16 at equal width / depth: prefill and decode tokens/s, kernel table")
 E2E_REQUESTS = 8          # per replica (2 for stochastic32k: a 30k-token prefill and PCIe-bound verifies per request)
 
 
@@ -484,6 +487,9 @@ def main():
     import torch
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py measures the CUDA path: no GPU is visible (there is no CPU fallback)")
+    if args.workload == "radanex":
+        from umbrella_b200 import seq_bench
+        return seq_bench.run(args)
     run_ours(args)
 
 

@@ -28,6 +28,7 @@ struct Scratch {
     void* hs;          // act [T, width]
     float* proj;       // fp32 [T, max in-projection rows]
     float* o32;        // fp32 [T, max(heads vdim)]  retention outputs before the gate
+    float* rot;        // fp32 [T, max rot_dims]     the step's cos | sin table
     void* mixed;       // act [T, max(heads vdim)]   mixer output before W_o
     void* cq;          // act [T, max q_rank]
     void* c;           // act [T, max kv_rank]
@@ -49,12 +50,12 @@ struct Scratch {
 
 static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratch* s) {
     const size_t es = m->dtype == UMBS_F32 ? 4 : 2;
-    int in_rows = 1, hv = 1, qr = 1, kvr = 1, hd = 1, hkv = 1, top = 1, experts = 1, ff = 1, sff = 1;
+    int rotd = 1, in_rows = 1, hv = 1, qr = 1, kvr = 1, hd = 1, hkv = 1, top = 1, experts = 1, ff = 1, sff = 1;
     for (int i = 0; i < m->n_layers; ++i) {
         const umbs_layer_t& l = m->layers[i];
         auto up = [](int& a, int b) { if (b > a) a = b; };
         up(hv, l.heads * l.vdim);
-        if (l.mixer == UMBS_MIX_RETENTION) up(in_rows, 2 * l.heads * l.dim + 2 * l.heads * l.vdim);
+        if (l.mixer == UMBS_MIX_RETENTION) { up(in_rows, 2 * l.heads * l.dim + 2 * l.heads * l.vdim); up(rotd, l.rot_dims); }
         else {
             up(in_rows, l.q_rank + l.kv_rank);
             up(qr, l.q_rank); up(kvr, l.kv_rank); up(hd, l.heads * l.dim); up(hkv, l.heads * l.kv_rank);
@@ -70,6 +71,7 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
     z.hs = a.take(Tz * W * es);
     z.proj = (float*)a.take(Tz * in_rows * 4);
     z.o32 = (float*)a.take(Tz * hv * 4);
+    z.rot = (float*)a.take(Tz * rotd * 4);
     z.mixed = a.take(Tz * hv * es);
     z.cq = a.take(Tz * qr * es);
     z.c = a.take(Tz * kvr * es);
@@ -125,7 +127,7 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
             const int rows = 2 * l.heads * l.dim + 2 * hv;
             UMBS_TRY(umbs_gemm(dt, hs, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
             UMBS_TRY(umbs_retention(dt, s.proj, rows, b, l.heads, l.dim, l.vdim, l.rot_dims, l.inv_freq, l.decay,
-                                    m->norm_eps, l.ret_state, s.o32, s.mixed, stream));
+                                    m->norm_eps, l.ret_state, s.o32, s.rot, s.mixed, stream));
         } else if (l.mixer == UMBS_MIX_LATENT_ATTENTION) {
             const int rows = l.q_rank + l.kv_rank, hd = l.heads * l.dim, R = l.kv_rank;
             UMBS_TRY(umbs_gemm(dt, hs, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));

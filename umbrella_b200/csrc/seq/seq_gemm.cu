@@ -2,12 +2,14 @@
 // experts), optionally over expert-sorted gathered rows, optionally with the gated feed-forward activation fused
 // into the epilogue of a gate|up pair of products.
 //
-// Two kernels share one argument block:
+// Three kernels share one argument block:
 //   * gemm_simt_kernel  -- fp32 FMA chains over shared-memory tiles; the UMBS_F32 mode (true 32-bit) and every shape
 //                          the tensor-core kernel does not take (K not a multiple of 16, unaligned rows);
-//   * gemm_mma_kernel   -- bf16 operands through mma.sync.m16n8k16 with fp32 accumulators.
-// Both walk k from 0 upwards in one chain per output element, so a row's result is the same whatever else is in
-// the batch and however the prompt was cut.
+//   * gemm_mma_kernel   -- bf16 operands through mma.sync.m16n8k16 with fp32 accumulators;
+//   * gemm_skinny_kernel -- bf16, at most 16 rows (decoding): a weight stream with the rows' partial sums in registers.
+// In each of them an output element is one fp32 sum over k in an order that does not depend on the other rows, so a
+// row's result is the same whatever else is in the batch; which kernel runs depends on the row count, and the three
+// differ from each other by rounding only.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -209,6 +211,105 @@ __global__ void __launch_bounds__(256) gemm_mma_kernel(GemmArgs a) {
             }
 }
 
+// ------------------------------------------------------------------------------------------------ few rows (decode)
+// Up to 16 activation rows per group: the product is a stream over the weights.  A warp owns four weight rows (with
+// DUAL: the gate and up rows of two outputs) and walks k with one 16-byte load per lane and row, every row's load in
+// flight at once; the few activation rows come through L1.  Lanes keep fp32 partial sums per (weight row, activation
+// row) and a shuffle tree adds them at the end.  A group without rows returns before touching its weights, so a decode
+// step reads only the experts that were chosen.
+constexpr int SK_ROWS = 4, SK_WARPS = 4;
+
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+template <typename TC, bool DUAL, int MT>
+__global__ void __launch_bounds__(32 * SK_WARPS) gemm_skinny_kernel(GemmArgs a) {
+    const int g = blockIdx.z;
+    int row_lo = 0, rows = a.M;
+    if (a.grp_off != nullptr) { row_lo = a.grp_off[g]; rows = a.grp_off[g + 1] - row_lo; }
+    const int m0 = blockIdx.y * MT;
+    if (m0 >= rows) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int OUTS = DUAL ? SK_ROWS / 2 : SK_ROWS;           // outputs per warp
+    const int n0 = (blockIdx.x * SK_WARPS + warp) * OUTS;
+    if (n0 >= a.N) return;
+    const __nv_bfloat16* A = (const __nv_bfloat16*)a.A + (int64_t)g * a.a_goff;
+    const __nv_bfloat16* W = (const __nv_bfloat16*)a.W + (int64_t)g * a.w_gstride;
+    const __nv_bfloat16* wrow[SK_ROWS];
+#pragma unroll
+    for (int i = 0; i < SK_ROWS; ++i) {
+        int n = DUAL ? (n0 + (i >> 1)) : (n0 + i);
+        n = min(n, a.N - 1);                                      // a tail warp recomputes the last row; it is not stored
+        wrow[i] = W + (int64_t)(DUAL ? ((i & 1) * a.N + n) : n) * a.ldw;
+    }
+    const __nv_bfloat16* arow[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        const int p = row_lo + min(m0 + m, rows - 1);
+        arow[m] = A + (int64_t)(a.row_src ? a.row_src[p] : p) * a.lda;
+    }
+    float acc[SK_ROWS][MT] = {};
+    for (int k = lane * 8; k < a.K; k += 256) {
+        uint4 wv[SK_ROWS];
+#pragma unroll
+        for (int i = 0; i < SK_ROWS; ++i) wv[i] = __ldg(reinterpret_cast<const uint4*>(wrow[i] + k));
+        float wf[SK_ROWS][8];
+#pragma unroll
+        for (int i = 0; i < SK_ROWS; ++i) bf16x8_to_f32(wv[i], wf[i]);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float af[8];
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(arow[m] + k), af);
+#pragma unroll
+            for (int i = 0; i < SK_ROWS; ++i)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[i][m] = fmaf(af[e], wf[i][e], acc[i][m]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < SK_ROWS; ++i)
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc[i][m] += __shfl_xor_sync(0xffffffffu, acc[i][m], o);
+    TC* C = (TC*)a.C + (int64_t)g * a.c_goff;
+    if (lane == 0) {
+#pragma unroll
+        for (int o = 0; o < OUTS; ++o) {
+            if (n0 + o >= a.N) continue;
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                if (m0 + m >= rows) continue;
+                const float v = DUAL ? gated_act(acc[2 * o][m], acc[DUAL ? 2 * o + 1 : o][m], a.limit) : acc[o][m];
+                C[(int64_t)(row_lo + m0 + m) * a.ldc + n0 + o] = from_f32<TC>(v);
+            }
+        }
+    }
+}
+
+template <typename TC>
+static void launch_skinny(const GemmArgs& a, int groups, bool dual, cudaStream_t st) {
+    const int outs_per_block = SK_WARPS * (dual ? SK_ROWS / 2 : SK_ROWS);
+    const int mt = a.M <= 1 ? 1 : (a.M <= 2 ? 2 : (a.M <= 4 ? 4 : 8));
+    const dim3 grid((a.N + outs_per_block - 1) / outs_per_block, (a.M + mt - 1) / mt, groups), block(32 * SK_WARPS);
+#define UMBS_SK(MT)                                                                   \
+    do {                                                                              \
+        if (dual) gemm_skinny_kernel<TC, true, MT><<<grid, block, 0, st>>>(a);        \
+        else gemm_skinny_kernel<TC, false, MT><<<grid, block, 0, st>>>(a);            \
+    } while (0)
+    if (mt == 1) UMBS_SK(1);
+    else if (mt == 2) UMBS_SK(2);
+    else if (mt == 4) UMBS_SK(4);
+    else UMBS_SK(8);
+#undef UMBS_SK
+}
+
 template <typename TA, typename TC>
 static void launch_simt(const GemmArgs& a, int groups, bool dual, cudaStream_t st) {
     const dim3 grid((a.N + BN - 1) / BN, (a.M + BM - 1) / BM, groups);
@@ -237,9 +338,13 @@ extern "C" int umbs_gemm(int dtype, const void* A, int64_t lda, int a_goff, cons
         launch_simt<float, float>(a, groups, dual != 0, st);          // activations are fp32 too: c_f32 changes nothing
     } else if (dtype == UMBS_BF16) {
         // 16-byte loads: every row start and group offset must sit on a 16-byte boundary
-        const bool tc = (K % TK == 0) && (lda % 8 == 0) && (ldw % 8 == 0) && (a_goff % 8 == 0) && (w_gstride % 8 == 0) &&
-                        ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0);
-        if (tc) {
+        const bool vec = (K % 8 == 0) && (lda % 8 == 0) && (ldw % 8 == 0) && (a_goff % 8 == 0) && (w_gstride % 8 == 0) &&
+                         ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0);
+        const bool tc = vec && (K % TK == 0);
+        if (vec && M <= 16) {
+            if (c_f32) launch_skinny<float>(a, groups, dual != 0, st);
+            else launch_skinny<__nv_bfloat16>(a, groups, dual != 0, st);
+        } else if (tc) {
             if (c_f32) launch_mma<float>(a, groups, dual != 0, st);
             else launch_mma<__nv_bfloat16>(a, groups, dual != 0, st);
         } else {

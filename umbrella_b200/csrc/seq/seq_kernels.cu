@@ -115,66 +115,123 @@ __global__ void group_norm_rows_kernel(const float* __restrict__ x, const int32_
 }
 
 // ------------------------------------------------------------------------------------------------ retention
-// One block = (sequence, head, a slice of NC value columns).  The slice's part of the state, S[dim][NC], sits in
-// shared memory; thread j owns column j.  Tokens go in order; q and k of TB tokens at a time are rotated into
-// shared memory by the whole block.
+// cos / sin of every (token, frequency) pair of the step, once for all heads: tab[t] = cos[half] | sin[half]
+__global__ void rotary_table_kernel(const int32_t* __restrict__ tok_pos, const float* __restrict__ inv_freq, int half,
+                                    float* __restrict__ tab) {
+    const int t = blockIdx.x;
+    const float p = (float)tok_pos[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = p * inv_freq[i];
+        tab[(int64_t)t * 2 * half + i] = cosf(ang);
+        tab[(int64_t)t * 2 * half + half + i] = sinf(ang);
+    }
+}
+
+// One block = (sequence, head, 32 value columns).  Lane = column; warp w keeps rows [w DPT, (w + 1) DPT) of the
+// column's state in registers for the whole step.  Tokens go in order, TB at a time: the block rotates their q and k
+// into shared memory, every warp advances its slice of the state through the TB tokens and leaves its part of each
+// output in shared memory, and the parts are added in warp order.
 constexpr int kRetTB = 8;
+template <int DPT>
 __global__ void retention_kernel(const float* __restrict__ qkvg, int64_t ld, Batch b, int heads, int dim, int vdim,
-                                 int rot_dims, const float* __restrict__ inv_freq, const float* __restrict__ decay,
+                                 int rot_dims, const float* __restrict__ rot_tab, const float* __restrict__ decay,
                                  float* __restrict__ state, float* __restrict__ o_out) {
-    extern __shared__ float sm[];
-    const int NC = blockDim.x;
-    float* S = sm;                         // [dim][NC]
-    float* qs = S + (size_t)dim * NC;      // [TB][dim]
-    float* ks = qs + kRetTB * dim;         // [TB][dim]
-    const int s = blockIdx.x, h = blockIdx.y, j = blockIdx.z * NC + threadIdx.x;
+    extern __shared__ __align__(16) float sm[];
+    const int DS = blockDim.y, dimP = DS * DPT, nthr = 32 * DS;
+    float* qs = sm;                          // [TB][dimP]
+    float* ks = qs + kRetTB * dimP;          // [TB][dimP]
+    float* part = ks + kRetTB * dimP;        // [DS][TB][32]
+    const int s = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, w = threadIdx.y, tid = w * 32 + lane;
+    const int j = blockIdx.z * 32 + lane, d0 = w * DPT;
     const int start = b.seq_start[s], len = b.seq_len[s], pos0 = b.seq_pos0[s], slot = b.seq_slot[s];
     const bool col = j < vdim;
     const float dec = decay[h];
     const float kscale = 1.f / sqrtf((float)dim);
     const int half = rot_dims / 2;
     float* st = state + (((int64_t)slot * heads + h) * dim) * vdim;
-    for (int d = 0; d < dim; ++d) S[d * NC + threadIdx.x] = (col && pos0 > 0) ? st[(int64_t)d * vdim + j] : 0.f;
+    float S[DPT];
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) S[i] = (col && pos0 > 0 && d0 + i < dim) ? st[(int64_t)(d0 + i) * vdim + j] : 0.f;
     const int qoff = h * dim, koff = heads * dim + h * dim, voff = 2 * heads * dim + h * vdim;
+    // Each thread stages EPT (token, dim) elements of q and k and up to TB values of v per round; the loads of round
+    // r + 1 are issued before round r is consumed, so their latency hides behind the serial walk through the tokens.
+    constexpr int EPT = kRetTB * DPT / 32;
+    float* vs = part + DS * kRetTB * 32;     // [TB][32]
+    float pq[EPT], pq2[EPT], pk[EPT], pk2[EPT], pc[EPT], ps[EPT], pv[kRetTB];
+    auto fetch = [&](int t0) {
+        const int nb = min(kRetTB, len - t0);
+#pragma unroll
+        for (int e = 0; e < EPT; ++e) {
+            const int i = tid + e * nthr, tt = i / dimP, d = i - tt * dimP;
+            pq[e] = pk[e] = pq2[e] = pk2[e] = ps[e] = 0.f;
+            pc[e] = 1.f;
+            if (tt < nb && d < dim) {
+                const int64_t tok = start + t0 + tt;
+                const float* row = qkvg + tok * ld;
+                pq[e] = row[qoff + d];
+                pk[e] = row[koff + d];
+                if (d < rot_dims) {
+                    const float* cs = rot_tab + tok * rot_dims;
+                    const int partner = d < half ? d + half : d - half, f = d < half ? d : d - half;
+                    pq2[e] = row[qoff + partner];
+                    pk2[e] = row[koff + partner];
+                    pc[e] = cs[f];
+                    ps[e] = d < half ? -cs[half + f] : cs[half + f];
+                }
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < kRetTB; ++e) {
+            const int i = tid + e * nthr, tt = i >> 5, jj = blockIdx.z * 32 + (i & 31);
+            pv[e] = (i < nb * 32 && jj < vdim) ? qkvg[(int64_t)(start + t0 + tt) * ld + voff + jj] : 0.f;
+        }
+    };
+    fetch(0);
     for (int t0 = 0; t0 < len; t0 += kRetTB) {
         const int nb = min(kRetTB, len - t0);
         __syncthreads();
-        for (int i = threadIdx.x; i < nb * dim; i += NC) {
-            const int tt = i / dim, d = i - tt * dim;
-            const float* row = qkvg + (int64_t)(start + t0 + tt) * ld;
-            float q = row[qoff + d], k = row[koff + d];
-            if (d < rot_dims) {
-                const int fi = d < half ? d : d - half;
-                const float ang = (float)(pos0 + t0 + tt) * inv_freq[fi];
-                const float c = cosf(ang), sn = sinf(ang);
-                if (d < half) {
-                    q = q * c - row[qoff + d + half] * sn;
-                    k = k * c - row[koff + d + half] * sn;
-                } else {
-                    q = q * c + row[qoff + d - half] * sn;
-                    k = k * c + row[koff + d - half] * sn;
-                }
-            }
-            qs[tt * dim + d] = q;
-            ks[tt * dim + d] = k * kscale;
+#pragma unroll
+        for (int e = 0; e < EPT; ++e) {
+            const int i = tid + e * nthr;
+            qs[i] = pq[e] * pc[e] + pq2[e] * ps[e];                 // (u cos - v sin) for the first half, (v cos + u sin) for the second
+            ks[i] = (pk[e] * pc[e] + pk2[e] * ps[e]) * kscale;
+        }
+#pragma unroll
+        for (int e = 0; e < kRetTB; ++e) {
+            const int i = tid + e * nthr;
+            if (i < kRetTB * 32) vs[i] = pv[e];
         }
         __syncthreads();
-        if (col) {
-            for (int tt = 0; tt < nb; ++tt) {
-                const int64_t tok = start + t0 + tt;
-                const float v = qkvg[tok * ld + voff + j];
-                float acc = 0.f;
-                for (int d = 0; d < dim; ++d) {
-                    const float sv = dec * S[d * NC + threadIdx.x] + ks[tt * dim + d] * v;
-                    S[d * NC + threadIdx.x] = sv;
-                    acc += sv * qs[tt * dim + d];
-                }
-                o_out[tok * ((int64_t)heads * vdim) + h * vdim + j] = acc;
+        if (t0 + kRetTB < len) fetch(t0 + kRetTB);
+        for (int tt = 0; tt < nb; ++tt) {
+            const float v = vs[tt * 32 + lane];
+            const float4* k4 = reinterpret_cast<const float4*>(ks + tt * dimP + d0);
+            const float4* q4 = reinterpret_cast<const float4*>(qs + tt * dimP + d0);
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < DPT / 4; ++i) {
+                const float4 kv = k4[i], qv = q4[i];
+                S[4 * i + 0] = fmaf(dec, S[4 * i + 0], kv.x * v); acc = fmaf(S[4 * i + 0], qv.x, acc);
+                S[4 * i + 1] = fmaf(dec, S[4 * i + 1], kv.y * v); acc = fmaf(S[4 * i + 1], qv.y, acc);
+                S[4 * i + 2] = fmaf(dec, S[4 * i + 2], kv.z * v); acc = fmaf(S[4 * i + 2], qv.z, acc);
+                S[4 * i + 3] = fmaf(dec, S[4 * i + 3], kv.w * v); acc = fmaf(S[4 * i + 3], qv.w, acc);
             }
+            part[(w * kRetTB + tt) * 32 + lane] = acc;
+        }
+        __syncthreads();
+        for (int i = tid; i < nb * 32; i += nthr) {
+            const int tt = i >> 5, l = i & 31, jj = blockIdx.z * 32 + l;
+            if (jj >= vdim) continue;
+            float o = 0.f;
+            for (int ww = 0; ww < DS; ++ww) o += part[(ww * kRetTB + tt) * 32 + l];
+            o_out[(int64_t)(start + t0 + tt) * ((int64_t)heads * vdim) + h * vdim + jj] = o;
         }
     }
-    if (col)
-        for (int d = 0; d < dim; ++d) st[(int64_t)d * vdim + j] = S[d * NC + threadIdx.x];
+    if (col) {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i)
+            if (d0 + i < dim) st[(int64_t)(d0 + i) * vdim + j] = S[i];
+    }
 }
 
 // o / rms(o) per head, times silu(g); one warp per (token, head)
@@ -216,61 +273,149 @@ __global__ void latent_norm_kernel(const float* __restrict__ x, int q_rank, int 
         c[(int64_t)t * kv_rank + e] = from_f32<T>(xr[q_rank + e] * ik * kw[e]);
 }
 
-// One warp per (token, head).  Lane l scores key jlo + 32 i + l; the output's kv_rank components are spread over the
-// lanes (component r on lane r mod 32), RPL per lane.
+// Tiled form.  One block = 32 consecutive (token, head) rows of ONE sequence (token-major), 8 warps x 4 rows.  The keys
+// the rows can see are walked in tiles of 32; a tile's latents are converted to fp32 in shared memory once and serve
+// every row of the block -- all heads share them, as do neighbouring tokens, whose windows differ by one key.
+//   scores:  lane = key; each lane walks its key's latent and the warp's four query rows 4 floats at a time
+//   softmax: running maximum / sum per row (fp32), rescaling the accumulators when the maximum moves
+//   values:  lane owns components lane, lane + 32, ...; the tile's weights reach it by shuffle
+constexpr int kLaRows = 32, kLaKeys = 32, kLaQH = 4;
+__device__ __forceinline__ void unpack16(const uint4& v, float* dst, const float*) {
+    *reinterpret_cast<float4*>(dst) = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z),
+                                                  __uint_as_float(v.w));
+}
+__device__ __forceinline__ void unpack16(const uint4& v, float* dst, const __nv_bfloat16*) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+    *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
 template <typename T, int RPL>
-__global__ void latent_attention_kernel(const float* __restrict__ q_abs, const T* __restrict__ c, const T* __restrict__ ring,
-                                        int ring_len, Batch b, int heads, int R, int window, float scale,
-                                        T* __restrict__ out) {
-    extern __shared__ float sm[];          // [warps][R] queries
-    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int w = blockIdx.x * (blockDim.x >> 5) + wib;
-    if (w >= b.n_tokens * heads) return;
-    const int t = w / heads, h = w - t * heads;
-    float* q = sm + (size_t)wib * R;
-    for (int r = lane; r < R; r += 32) q[r] = q_abs[((int64_t)t * heads + h) * R + r];
-    __syncwarp();
-    const int s = b.tok_seq[t], pos = b.tok_pos[t];
-    const int start = b.seq_start[s], pos0 = b.seq_pos0[s], slot = b.seq_slot[s];
+__global__ void __launch_bounds__(256) latent_attention_kernel(const float* __restrict__ q_abs, const T* __restrict__ c,
+                                                               const T* __restrict__ ring, int ring_len, Batch b, int heads,
+                                                               int R, int window, float scale, int rpb, int vec,
+                                                               T* __restrict__ out) {
+    extern __shared__ __align__(16) float sm[];
+    const int RS = ((R + 3) & ~3) + 4;                 // row stride: 16-byte rows, lanes 4 banks apart
+    float* qs = sm;                                    // [32][RS]
+    float* cs = sm + (size_t)kLaRows * RS;             // [32][RS]
+    const int s = blockIdx.y;
+    const int len = b.seq_len[s], start = b.seq_start[s], pos0 = b.seq_pos0[s], slot = b.seq_slot[s];
+    // rpb rows of the 32 are used: a decode step has few rows per sequence and spreads them over more blocks
+    const int row0 = blockIdx.x * rpb, nrows = min(len * heads, row0 + rpb);
+    if (row0 >= nrows) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const T* rbase = ring + (int64_t)slot * ring_len * R;
-    const int jlo = max(0, pos - window + 1);
-    float m = -INFINITY, l = 0.f, acc[RPL];
+    // queries of the block's rows, zero beyond R and beyond the sequence
+    for (int i = threadIdx.x; i < kLaRows * RS; i += blockDim.x) {
+        const int rr = i / RS, r = i - rr * RS, row = row0 + rr;
+        float v = 0.f;
+        if (row < nrows && r < R) v = q_abs[((int64_t)(start + row / heads) * heads + row % heads) * R + r];
+        qs[i] = v;
+    }
+    int rpos[kLaQH];                                    // position of each of the warp's rows, -1 = no such row
+    float m[kLaQH], l[kLaQH], acc[kLaQH][RPL];
 #pragma unroll
-    for (int i = 0; i < RPL; ++i) acc[i] = 0.f;
-    for (int j0 = jlo; j0 <= pos; j0 += 32) {
-        const int j = j0 + lane;
-        const T* row = nullptr;
-        if (j <= pos) row = j >= pos0 ? c + (int64_t)(start + j - pos0) * R : rbase + (int64_t)(j % ring_len) * R;
-        float sc = -INFINITY;
-        if (row != nullptr) {
-            float d = 0.f;
-            for (int r = 0; r < R; ++r) d += q[r] * to_f32(row[r]);
-            sc = d * scale;
+    for (int a = 0; a < kLaQH; ++a) {
+        const int row = row0 + warp * kLaQH + a;
+        rpos[a] = row < nrows ? pos0 + row / heads : -1;
+        m[a] = -INFINITY;
+        l[a] = 0.f;
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) acc[a][i] = 0.f;
+    }
+    const int pos_first = pos0 + row0 / heads, pos_last = pos0 + (min(row0 + kLaRows, nrows) - 1) / heads;
+    const int jlo = max(0, pos_first - window + 1);
+    for (int j0 = jlo; j0 <= pos_last; j0 += kLaKeys) {
+        __syncthreads();                                // the previous tile (and, first time round, qs) is done with
+        if (vec) {
+            // 16-byte pieces, every thread's loads of the tile in flight together
+            constexpr int EP = 16 / sizeof(T);
+            const int ppr = R / EP, pieces = kLaKeys * ppr;
+#pragma unroll 4
+            for (int i = threadIdx.x; i < pieces; i += 256) {
+                const int kk = i / ppr, e0 = (i - kk * ppr) * EP, j = j0 + kk;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (j <= pos_last) {
+                    const T* src = j >= pos0 ? c + (int64_t)(start + j - pos0) * R : rbase + (int64_t)(j % ring_len) * R;
+                    v = *reinterpret_cast<const uint4*>(src + e0);
+                }
+                unpack16(v, cs + kk * RS + e0, (const T*)nullptr);
+            }
+            if (threadIdx.x < kLaKeys) {
+                for (int r = R; r < RS; ++r) cs[threadIdx.x * RS + r] = 0.f;
+            }
+        } else {
+            for (int kk = warp; kk < kLaKeys; kk += 8) {
+                const int j = j0 + kk;
+                const T* src = nullptr;
+                if (j <= pos_last) src = j >= pos0 ? c + (int64_t)(start + j - pos0) * R : rbase + (int64_t)(j % ring_len) * R;
+                for (int r = lane; r < RS; r += 32) cs[kk * RS + r] = (src != nullptr && r < R) ? to_f32(src[r]) : 0.f;
+            }
         }
-        const float mn = fmaxf(m, warp_max(sc));
-        const float corr = expf(m - mn);            // m = -inf on the first tile: exp(-inf) = 0
-        const float p = row != nullptr ? expf(sc - mn) : 0.f;
-        l = l * corr + warp_sum(p);
-        m = mn;
+        __syncthreads();
+        // does any of the warp's rows see any key of this tile?
+        bool any = false;
 #pragma unroll
-        for (int i = 0; i < RPL; ++i) acc[i] *= corr;
-        const int nk = min(32, pos - j0 + 1);
-        for (int jj = 0; jj < nk; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, p, jj);
-            const int jk = j0 + jj;
-            const T* rj = jk >= pos0 ? c + (int64_t)(start + jk - pos0) * R : rbase + (int64_t)(jk % ring_len) * R;
+        for (int a = 0; a < kLaQH; ++a) any |= rpos[a] >= j0 && rpos[a] - window + 1 <= j0 + kLaKeys - 1;
+        if (!any) continue;
+        float sc[kLaQH] = {};
+        const float4* ck = reinterpret_cast<const float4*>(cs + lane * RS);
+        const float4* q4 = reinterpret_cast<const float4*>(qs + warp * kLaQH * RS);
+        const int n4 = (R + 3) >> 2, rs4 = RS >> 2;
+        for (int r = 0; r < n4; ++r) {
+            const float4 cv = ck[r];
+#pragma unroll
+            for (int a = 0; a < kLaQH; ++a) {
+                const float4 qv = q4[a * rs4 + r];
+                sc[a] = fmaf(qv.x, cv.x, fmaf(qv.y, cv.y, fmaf(qv.z, cv.z, fmaf(qv.w, cv.w, sc[a]))));
+            }
+        }
+        const int j = j0 + lane;
+        float p[kLaQH];
+#pragma unroll
+        for (int a = 0; a < kLaQH; ++a) {
+            const bool vis = rpos[a] >= 0 && j <= rpos[a] && j > rpos[a] - window;
+            const float v = vis ? sc[a] * scale : -INFINITY;
+            const float mn = fmaxf(m[a], warp_max(v));
+            if (mn == -INFINITY) { p[a] = 0.f; continue; }          // the row sees nothing yet
+            const float corr = expf(m[a] - mn);
+            p[a] = vis ? expf(v - mn) : 0.f;
+            l[a] = l[a] * corr + warp_sum(p[a]);
+            m[a] = mn;
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) acc[a][i] *= corr;
+        }
+        for (int kk = 0; kk < kLaKeys; ++kk) {
+            float pk[kLaQH];
+#pragma unroll
+            for (int a = 0; a < kLaQH; ++a) pk[a] = __shfl_sync(0xffffffffu, p[a], kk);
+            const float* cr = cs + kk * RS;
 #pragma unroll
             for (int i = 0; i < RPL; ++i) {
                 const int r = lane + 32 * i;
-                if (r < R) acc[i] += pj * to_f32(rj[r]);
+                const float cv = r < R ? cr[r] : 0.f;
+#pragma unroll
+                for (int a = 0; a < kLaQH; ++a) acc[a][i] = fmaf(pk[a], cv, acc[a][i]);
             }
         }
     }
-    const float invl = 1.f / l;
 #pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-        const int r = lane + 32 * i;
-        if (r < R) out[((int64_t)t * heads + h) * R + r] = from_f32<T>(acc[i] * invl);
+    for (int a = 0; a < kLaQH; ++a) {
+        const int row = row0 + warp * kLaQH + a;
+        if (row >= nrows) continue;
+        const float inv = 1.f / l[a];
+        T* o = out + ((int64_t)(start + row / heads) * heads + row % heads) * R;
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) {
+            const int r = lane + 32 * i;
+            if (r < R) o[r] = from_f32<T>(acc[a][i] * inv);
+        }
     }
 }
 
@@ -418,29 +563,43 @@ extern "C" int umbs_group_norm_rows(int dtype, const float* x, const int32_t* ro
     return (int)cudaGetLastError();
 }
 
+template <int DPT>
+static int launch_retention(const float* qkvg, int64_t ld, const Batch& b, int heads, int dim, int vdim, int rot_dims,
+                            const float* rot_tab, const float* decay, float* state, float* o, cudaStream_t st) {
+    const int ds = (dim + DPT - 1) / DPT;
+    const dim3 grid(b.n_seqs, heads, (vdim + 31) / 32), block(32, ds);
+    const size_t smem = ((size_t)2 * kRetTB * ds * DPT + (size_t)ds * kRetTB * 32 + kRetTB * 32) * sizeof(float);
+    static size_t set = 0;
+    if (smem > 48 * 1024 && smem > set) {
+        cudaError_t e = cudaFuncSetAttribute(retention_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        set = smem;
+    }
+    retention_kernel<DPT><<<grid, block, smem, st>>>(qkvg, ld, b, heads, dim, vdim, rot_dims, rot_tab, decay, state, o);
+    return 0;
+}
+
 extern "C" int umbs_retention(int dtype, const float* qkvg, int64_t ld, const umbs_batch_t* batch, int heads, int dim,
                               int vdim, int rot_dims, const float* inv_freq, const float* decay, float eps, float* state,
-                              float* o_scratch, void* out, umbs_stream_t stream) {
+                              float* o_scratch, float* rot_scratch, void* out, umbs_stream_t stream) {
     if (batch->n_tokens <= 0) return 0;
     if (rot_dims < 0 || rot_dims > dim || (rot_dims & 1)) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    // columns per block: as many as keep the state slice in shared memory, at most 128
-    int nc = 128;
-    while (nc > 32 && (nc / 2 >= vdim || ((size_t)dim * nc + 2 * kRetTB * dim) * sizeof(float) > 200 * 1024)) nc /= 2;
-    const size_t smem = ((size_t)dim * nc + 2 * kRetTB * dim) * sizeof(float);
-    if (smem > 220 * 1024) return UMB_ERR_UNSUPPORTED;
-    static size_t smem_set = 0;
-    if (smem > 48 * 1024 && smem > smem_set) {
-        cudaError_t e = cudaFuncSetAttribute(retention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        smem_set = smem;
+    unsigned launches = 2;
+    if (rot_dims > 0) {
+        rotary_table_kernel<<<batch->n_tokens, 64, 0, st>>>(batch->tok_pos, inv_freq, rot_dims / 2, rot_scratch);
+        ++launches;
     }
-    dim3 grid(batch->n_seqs, heads, (vdim + nc - 1) / nc);
-    retention_kernel<<<grid, nc, smem, st>>>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, inv_freq, decay, state, o_scratch);
+    int rc;
+    if (dim <= 32) rc = launch_retention<8>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_scratch, decay, state, o_scratch, st);
+    else if (dim <= 128) rc = launch_retention<16>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_scratch, decay, state, o_scratch, st);
+    else if (dim <= 512) rc = launch_retention<32>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_scratch, decay, state, o_scratch, st);
+    else return UMB_ERR_UNSUPPORTED;
+    if (rc) return rc;
     const int warps = batch->n_tokens * heads;
     UMBS_DISPATCH_T(dtype, retention_gate_kernel<T><<<(warps + 3) / 4, 128, 0, st>>>(o_scratch, qkvg, ld, batch->n_tokens,
                                                                                    heads, dim, vdim, eps, (T*)out));
-    count_launches(2);
+    count_launches(launches);
     return (int)cudaGetLastError();
 }
 
@@ -457,10 +616,23 @@ extern "C" int umbs_latent_norm(int dtype, const float* x, int n, int q_rank, in
 template <typename T>
 static int launch_latent_attention(const float* q_abs, const void* c, const void* ring, int ring_len, const Batch& b,
                                    int heads, int R, int window, float scale, void* out, cudaStream_t st) {
-    const int warps = b.n_tokens * heads, wpb = 4;
-    const dim3 grid((warps + wpb - 1) / wpb), block(32 * wpb);
-    const size_t smem = (size_t)wpb * R * sizeof(float);
-#define UMBS_LA(RPL) latent_attention_kernel<T, RPL><<<grid, block, smem, st>>>(q_abs, (const T*)c, (const T*)ring, ring_len, b, heads, R, window, scale, (T*)out)
+    const int rpb = b.max_seq_len == 1 ? 8 : kLaRows;
+    const int ep = 16 / (int)sizeof(T);
+    const int vec = (R % ep == 0) && ((uintptr_t)c % 16 == 0) && ((uintptr_t)ring % 16 == 0);
+    const dim3 grid((b.max_seq_len * heads + rpb - 1) / rpb, b.n_seqs), block(256);
+    const size_t smem = (size_t)2 * kLaRows * (((R + 3) & ~3) + 4) * sizeof(float);
+#define UMBS_LA(RPL)                                                                                                   \
+    do {                                                                                                               \
+        static size_t set = 0;                                                                                         \
+        if (smem > 48 * 1024 && smem > set) {                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(latent_attention_kernel<T, RPL>,                                      \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
+            if (e != cudaSuccess) return (int)e;                                                                       \
+            set = smem;                                                                                                \
+        }                                                                                                              \
+        latent_attention_kernel<T, RPL><<<grid, block, smem, st>>>(q_abs, (const T*)c, (const T*)ring, ring_len, b,    \
+                                                                   heads, R, window, scale, rpb, vec, (T*)out);        \
+    } while (0)
     if (R <= 32) UMBS_LA(1);
     else if (R <= 64) UMBS_LA(2);
     else if (R <= 128) UMBS_LA(4);

@@ -81,7 +81,8 @@ class SeqStateModel:
     """Weights + state cache + workspace of one sequence-state decoder on one GPU."""
 
     def __init__(self, spec: SeqModelSpec, device="cuda:0", dtype=torch.bfloat16, slots: int = 8,
-                 max_length: int | None = None, max_tokens: int = 0, model_name: str | None = None):
+                 max_length: int | None = None, max_tokens: int = 0, model_name: str | None = None,
+                 graph_decode: bool = True):
         if dtype not in (torch.bfloat16, torch.float32):
             raise TypeError("sequence-state decoders run in bfloat16 or float32")
         self.spec = self.config = spec
@@ -98,8 +99,12 @@ class SeqStateModel:
         self._c_version = -1
         self._ws = None
         self._ws_tokens = self._ws_want = 0
-        self._pinned = None
-        self._dev_ints = None
+        # decode steps (one token per sequence) replay a CUDA graph of the whole step, captured per batch size once that
+        # size has run eagerly twice: slots, positions and parities live in the device-side batch description, so the
+        # same graph serves every later step of that size
+        self.graph_decode = graph_decode
+        self._graphs: dict = {}
+        self._graph_seen: dict = {}
 
     # ------------------------------------------------------------------ allocation
     def alloc(self, **kwargs):
@@ -251,25 +256,63 @@ class SeqStateModel:
             raise ValueError("a slot appears twice in one step")
         flat = ids + tok_seq + tok_pos + slot + start + length + pos0 + parity + want
         host = torch.tensor(flat, dtype=torch.int32).pin_memory()
-        dev = host.to(self.device, non_blocking=True)
         self._reserve(max(T, self._max_tokens0), max(Wn, 1))       # sized once for the largest step announced
-        base, o = dev.data_ptr(), 0
-        bt = S.Batch()
-        bt.n_tokens, bt.n_seqs, bt.n_want, bt.max_seq_len = T, B, Wn, max(length)
-        for name, n in (("tok_ids", T), ("tok_seq", T), ("tok_pos", T), ("seq_slot", B), ("seq_start", B), ("seq_len", B),
-                        ("seq_pos0", B), ("seq_parity", B), ("want_rows", Wn)):
-            setattr(bt, name, base + 4 * o)
-            o += n
-        logits = torch.empty((Wn, self.spec.vocab), dtype=torch.float32, device=self.device)
-        layers = torch.empty((self.num_layers, T, self.spec.width), dtype=torch.float32, device=self.device) \
-            if layer_out else None
-        S.check(S.load().umbs_forward(C.byref(self._model_struct()), C.byref(bt), logits.data_ptr() if Wn else None,
-                                      layers.data_ptr() if layer_out else None, self._ws.data_ptr(), self._ws.numel(),
-                                      torch.cuda.current_stream().cuda_stream), "forward")
-        self._keep = (host, dev)              # alive until the next step is enqueued behind this one
+        model = self._model_struct()
+
+        def describe(base):
+            bt, o = S.Batch(), 0
+            bt.n_tokens, bt.n_seqs, bt.n_want, bt.max_seq_len = T, B, Wn, max(length)
+            for name, n in (("tok_ids", T), ("tok_seq", T), ("tok_pos", T), ("seq_slot", B), ("seq_start", B),
+                            ("seq_len", B), ("seq_pos0", B), ("seq_parity", B), ("want_rows", Wn)):
+                setattr(bt, name, base + 4 * o)
+                o += n
+            return bt
+
+        def enqueue(bt, logits, layers=None):
+            S.check(S.load().umbs_forward(C.byref(model), C.byref(bt), logits.data_ptr() if Wn else None,
+                                          layers.data_ptr() if layers is not None else None, self._ws.data_ptr(),
+                                          self._ws.numel(), torch.cuda.current_stream().cuda_stream), "forward")
+
+        logits = None
+        if self.graph_decode and T == B and Wn > 0 and not layer_out:
+            logits = self._graph_step((B, Wn, cache.version, self._ws.data_ptr()), host, describe, enqueue)
+        layers = None
+        if logits is None:
+            dev = host.to(self.device, non_blocking=True)
+            logits = torch.empty((Wn, self.spec.vocab), dtype=torch.float32, device=self.device)
+            layers = torch.empty((self.num_layers, T, self.spec.width), dtype=torch.float32, device=self.device) \
+                if layer_out else None
+            enqueue(describe(dev.data_ptr()), logits, layers)
+            self._keep = (host, dev)          # alive until the next step is enqueued behind this one
         for s, n in zip(slot, length):
             cache.advance(s, n)
         return (logits, layers) if layer_out else logits
+
+    def _graph_step(self, key, host, describe, enqueue):
+        """Replay (capturing first, on the third step of this shape) the CUDA graph of a decode step; None = run eagerly."""
+        g = self._graphs.get(key)
+        if g is None:
+            seen = self._graph_seen.get(key, 0)
+            self._graph_seen[key] = seen + 1
+            if seen < 2:
+                return None
+            for old in [k for k in self._graphs if k[2:] != key[2:]]:      # the cache or the workspace moved
+                del self._graphs[old]
+            ints = torch.empty(host.numel(), dtype=torch.int32, device=self.device)
+            out = torch.empty((key[1], self.spec.vocab), dtype=torch.float32, device=self.device)
+            bt = describe(ints.data_ptr())
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.graph(graph, stream=side):
+                enqueue(bt, out)
+            torch.cuda.current_stream().wait_stream(side)
+            g = self._graphs[key] = (graph, ints, out)
+        graph, ints, out = g
+        ints.copy_(host, non_blocking=True)
+        graph.replay()
+        self._keep = (host,)
+        return out.clone()
 
     def clear(self):
         self.cache.clear()

@@ -89,8 +89,10 @@ def retention(qkvg, batch: RaggedBatch, heads, dim, vdim, rot_dims, inv_freq, de
     T = qkvg.shape[0]
     o32 = torch.empty((T, heads * vdim), dtype=torch.float32, device=qkvg.device)
     out = torch.empty((T, heads * vdim), dtype=dtype, device=qkvg.device)
+    rot = torch.empty((T, max(rot_dims, 1)), dtype=torch.float32, device=qkvg.device)
     S.check(S.load().umbs_retention(_mode(out), _p(qkvg), qkvg.stride(0), C.byref(batch.c), heads, dim, vdim, rot_dims,
-                                    _p(inv_freq), _p(decay), float(eps), _p(state), _p(o32), _p(out), _stream()), "retention")
+                                    _p(inv_freq), _p(decay), float(eps), _p(state), _p(o32), _p(rot), _p(out), _stream()),
+            "retention")
     return out
 
 

@@ -1,0 +1,252 @@
+"""Throughput of the sequence-state decoder family beside the framework's Llama at equal size (``bench.py --workload
+radanex``): prefill and decode tokens/s of whole models with seeded random weights at layer sizes a real model has,
+and the device time of each mechanism's kernels against its roofline, next to the like kernel of the Llama path.
+
+Timing: CUDA events on the launching stream, 3 warm-up runs, a write over a buffer larger than L2 between timed runs
+of the kernel table (the whole-model runs read more than L2 by themselves), synchronize on both sides.
+"""
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _peaks():
+    try:
+        p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return 6650.0, 1590.0, "fallback"
+
+
+def radanex_config(width: int, layers: int = 8) -> dict:
+    """A Radanex config with the layer sizes of a model of this width: every fourth layer latent attention."""
+    heads = width // 128
+    ret = dict(type="retention", mixer=dict(heads=heads, dim=64, vdim=128, rot=dict(dims=64, base=1e6),
+                                           decay=[1 - 2.0 ** (-5 - (3 * h) // heads) for h in range(heads)]))
+    lat = dict(type="latent_attention", mixer=dict(heads=heads, dim=64, vdim=128, q_rank=3 * width // 8, kv_rank=width // 4,
+                                                   scale=0.125, mask=dict(size=1024)))
+    mlp = dict(kind="moe", router=dict(experts=16, top=2), expert=dict(ff=width // 2, limit=7.0),
+               shared=dict(ff=width, limit=7.0))
+    return dict(architecture="Radanex", width=width, vocab=32768, norm=dict(eps=1e-6, groups=4),
+                layers=[dict(lat if i % 4 == 3 else ret, mlp=mlp) for i in range(layers)])
+
+
+class Timer:
+    def __init__(self, device):
+        self.flush = torch.empty(192 << 20, dtype=torch.uint8, device=device)      # > the 126 MB L2
+
+    def __call__(self, fn, reps=5, warm=3, flush=True):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(reps):
+            if flush:
+                self.flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            total += s.elapsed_time(e)
+        return total / reps
+
+
+def bench_radanex(width, layers, device, prompt, ctx, batches, timer):
+    from .models.radanex import Radanex, spec_from_config
+    spec = spec_from_config(radanex_config(width, layers))
+    m = Radanex(spec, device=device, dtype=torch.bfloat16, slots=max(batches))
+    m.alloc()
+    m.load_synthetic(7)
+    g = torch.Generator().manual_seed(0)
+    toks = lambda n: torch.randint(0, spec.vocab, (n,), generator=g).tolist()
+    out = {"weight_gb": m.weight_bytes() / 1e9, "state_mb_per_sequence": m.cache.state_bytes_per_slot() / 1e6}
+
+    def prefill(n_seq):
+        ps = [toks(prompt) for _ in range(n_seq)]
+
+        def run():
+            slots = [m.cache.alloc_slot() for _ in ps]
+            m.forward([(s, p, [prompt - 1]) for s, p in zip(slots, ps)])
+            for s in slots:
+                m.cache.free_slot(s)
+        return run
+    for n_seq in (1, 4):
+        ms = timer(prefill(n_seq), reps=3, flush=False)
+        out[f"prefill_{n_seq}x{prompt}_tok_s"] = n_seq * prompt / ms * 1e3
+    for B in batches:
+        slots = [m.cache.alloc_slot() for _ in range(B)]
+        m.forward([(s, toks(ctx), []) for s in slots])
+        nxt = toks(B)
+        ms = timer(lambda: m.forward([(s, [t], [0]) for s, t in zip(slots, nxt)]), reps=20, flush=False)
+        out[f"decode_b{B}_tok_s"] = B / ms * 1e3
+        out[f"decode_b{B}_ms_per_step"] = ms
+        for s in slots:
+            m.cache.free_slot(s)
+    return m, out
+
+
+def bench_llama(width, layers, inter, device, prompt, ctx, timer):
+    from .models import llama as L
+    heads = width // 128
+    shape = L.LlamaShape(hidden_size=width, intermediate_size=inter, num_hidden_layers=layers, num_attention_heads=heads,
+                         num_key_value_heads=max(1, heads // 4), vocab_size=32768, rope_scaling=None, rope_theta=1e6)
+    m = L.SyntheticLlama(shape, max_length=prompt + ctx + 64, awq=False, seed=7, device=device, gen_device=device)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 32768, (prompt,), generator=g).to(device)
+    pos = torch.arange(prompt, device=device)
+    out = {"weight_gb": m.weight_bytes() / 1e9}
+
+    def prefill():
+        m.clear()
+        m.prefill_forward(ids, pos)
+    out[f"prefill_1x{prompt}_tok_s"] = prompt / timer(prefill, reps=3, flush=False) * 1e3
+    m.clear()
+    m.prefill_forward(ids[:ctx], pos[:ctx])
+    one, p1 = ids[:1].clone(), torch.tensor([ctx], device=device)
+
+    def decode():
+        m.kv_cache.kv_offset = ctx
+        m.prefill_forward(one, p1)
+    ms = timer(decode, reps=20, flush=False)
+    out["decode_b1_tok_s"], out["decode_b1_ms_per_step"] = 1e3 / ms, ms
+    return m, out
+
+
+def kernel_table(rm, lm, device, timer, T=4096):
+    """Device time of each mechanism at prefill size (T tokens) and at decode size (8 tokens), with its roofline
+    fraction: bytes / measured copy bandwidth, or FLOPs / measured bf16 GEMM throughput for the tensor-core products.
+    The fp32 mechanisms (recurrence, scores, norms) have no tensor-core peak to be held against: their bound is the
+    bytes they must move, which is what the fraction states."""
+    from . import ops, ops_seq as Q
+    hbm, tflops, how = _peaks()
+    sp = rm.spec
+    W = sp.width
+    ret = next(l for l in sp.layers if l.mixer == "retention")
+    lat = next(l for l in sp.layers if l.mixer == "latent_attention")
+    ri, li = sp.layers.index(ret), sp.layers.index(lat)
+    rw, lw = rm.weights[ri], rm.weights[li]
+    rows = []
+
+    def add(name, ms, nbytes=0, flops=0, like=None):
+        r = dict(kernel=name, ms=round(ms, 4))
+        if flops:
+            r["tflops"], r["frac_of_bf16_peak"] = round(flops / ms / 1e9, 1), round(flops / ms / 1e9 / tflops, 3)
+        if nbytes:
+            r["gb_s"], r["frac_of_hbm_peak"] = round(nbytes / ms / 1e6, 1), round(nbytes / ms / 1e6 / hbm, 3)
+        if like:
+            r["like"] = like
+        rows.append(r)
+    bf = dict(dtype=torch.bfloat16, device=device)
+    for n, tag in ((T, f"prefill T={T}"), (8, "decode T=8")):
+        nseq = 1 if n == T else 8
+        per = n // nseq
+        batch = Q.RaggedBatch([(s, per, 0 if n == T else 512, 0) for s in range(nseq)], device)
+        x = torch.randn(n, W, device=device)
+        h = torch.randn(n, W, **bf)
+        # dense projection (the retention in-projection) and the routed experts
+        w_in = rw["w_in"]
+        ms = timer(lambda: Q.gemm(h, w_in, out_f32=True))
+        add(f"gemm in-projection [{n} x {W}] x [{w_in.shape[0]} x {W}] ({tag})", ms, nbytes=w_in.numel() * 2 + n * W * 2 + n * w_in.shape[0] * 4,
+            flops=2 * n * W * w_in.shape[0])
+        f = ret.mlp
+        sel_w, grp_off, pair_tok, pair_pos, _ = Q.moe_route(h, rw["router"], f.top)
+        ms = timer(lambda: Q.gemm(h, rw["gu"], groups=f.experts, n=f.ff, dual=True, limit=f.limit, grp_off=grp_off, row_src=pair_tok,
+                                  rows=n * f.top, max_rows=n))
+        touched = min(f.experts, n * f.top)
+        add(f"gemm routed gate|up + activation, {f.experts} experts top {f.top} ({tag})", ms,
+            nbytes=touched * 2 * f.ff * W * 2 + n * W * 2 + n * f.top * f.ff * 2, flops=2 * n * f.top * W * 2 * f.ff)
+        ms = timer(lambda: Q.moe_route(h, rw["router"], f.top))
+        add(f"router + expert sort ({tag})", ms, nbytes=n * W * 2)
+        # norm + shift
+        st = rm.cache.shift[ri]
+        ms = timer(lambda: Q.group_norm_shift(x, rw["norm"], rw["shift"], st, batch, sp.norm_groups, sp.norm_eps, torch.bfloat16))
+        add(f"group norm + token shift ({tag})", ms, nbytes=n * W * (4 + 2 + 2))
+        # retention
+        ld = 2 * ret.heads * (ret.dim + ret.vdim)
+        qkvg = torch.randn(n, ld, device=device)
+        state = rm.cache.ret_state[ri]
+        ms = timer(lambda: Q.retention(qkvg, batch, ret.heads, ret.dim, ret.vdim, ret.rot_dims, rw["inv_freq"], rw["decay"],
+                                       sp.norm_eps, state, torch.bfloat16))
+        sbytes = nseq * ret.heads * ret.dim * ret.vdim * 4 * 2
+        add(f"retention: rotary + recurrence + unit norm + gate, fp32 ({tag})", ms,
+            nbytes=n * ld * 4 + n * ret.heads * ret.vdim * (4 + 4 + 2) + sbytes)
+        # latent attention
+        R = lat.kv_rank
+        qa = torch.randn(n, lat.heads * R, device=device)
+        c = torch.randn(n, R, **bf)
+        ring = rm.cache.ring[li]
+        ms = timer(lambda: Q.latent_attention(qa, c, ring, batch, lat.heads, lat.window, lat.scale, append=False))
+        keys = sum(min(p + 1, lat.window) for p in range(per)) * nseq if n == T else n * min(513, lat.window)
+        add(f"latent attention, window {lat.window}, fp32 scores ({tag})", ms,
+            nbytes=n * lat.heads * R * (4 + 2) + (n * R * 2 if n == T else keys * R * 2), flops=4 * keys * lat.heads * R)
+        # residual + depth mix
+        stack = torch.randn(len(sp.layers) + 1, n, W, device=device)
+        mix = torch.randn(n, W, device=device)
+        dw = rm.weights[-1]["depth"]
+        ms = timer(lambda: Q.depth_mix(x, mix, stack, len(sp.layers) - 1, dw, shared=mix))
+        add(f"residual + depth average over {len(sp.layers) + 1} streams ({tag})", ms, nbytes=n * W * 4 * (len(sp.layers) + 4))
+    # the like kernels of the Llama path: fp16 tcgen05 GEMM at its row limit, attention, rms norm
+    sh = lm.config
+    Hd, I = sh.hidden_size, sh.intermediate_size
+    lwt = lm.layer_weights[0]
+    f16 = dict(dtype=torch.float16, device=device)
+    for n in (128, 8):
+        xx = torch.randn(n, Hd, **f16)
+        y = torch.empty(n, I, **f16)
+        ms = timer(lambda: ops.gemm_f16(xx, lwt["wgu"], mode=ops.UMB_EPI_SILU_MUL, out=y, workspace=lm._gemm_ws))
+        add(f"llama gemm gate|up + silu [{n} x {Hd}] x [{2 * I} x {Hd}] (tcgen05)", ms, nbytes=2 * I * Hd * 2 + n * Hd * 2 + n * I * 2,
+            flops=2 * n * Hd * 2 * I, like="gemm")
+        ms = timer(lambda: ops.rmsnorm(xx, lwt["input_norm"], 1e-5))
+        add(f"llama rms norm, {n} rows", ms, nbytes=n * Hd * 4, like="group norm + token shift")
+    S = 2048
+    q = torch.randn(128, lm.num_heads, lm.head_dim, **f16)
+    k = torch.randn(S, lm.num_key_value_heads, lm.head_dim, **f16)
+    v = torch.randn_like(k)
+    ws = ops.tree_attn_workspace(128, lm.num_heads, lm.head_dim, device)
+    mask = ops.make_mask(ops.UMB_MASK_CAUSAL, prefix_len=S - 128)
+    ms = timer(lambda: ops.tree_attn(q, k, v, S, mask, "NHD", workspace=ws))
+    add(f"llama causal attention, 128 rows over {S} keys", ms, nbytes=2 * S * lm.num_key_value_heads * lm.head_dim * 2,
+        flops=4 * 128 * (S - 64) * lm.num_heads * lm.head_dim, like="latent attention")
+    q1 = q[:8].contiguous()
+    mask1 = ops.make_mask(ops.UMB_MASK_CAUSAL, prefix_len=S - 8)
+    ms = timer(lambda: ops.tree_attn(q1, k, v, S, mask1, "NHD", workspace=ws))
+    add(f"llama causal attention, 8 rows over {S} keys", ms, nbytes=2 * S * lm.num_key_value_heads * lm.head_dim * 2,
+        like="latent attention / retention (decode)")
+    return rows, how
+
+
+def run(args):
+    from . import _lib, _lib_seq
+    device = "cuda:0"
+    timer = Timer(device)
+    hbm, tflops, how = _peaks()
+    sizes = []
+    launches0 = _lib_seq.load().umbs_launch_count() + _lib.launch_count()
+    table = None
+    for width in (1024, 2048):
+        layers, prompt, ctx = 8, 2048, 512
+        rm, r = bench_radanex(width, layers, device, prompt, ctx, (1, 8, 64), timer)
+        lm, l = bench_llama(width, layers, 2 * width, device, prompt, ctx, timer)
+        sizes.append({"width": width, "layers": layers, "radanex_bf16": {k: round(v, 3) for k, v in r.items()},
+                      "llama_fp16": {k: round(v, 3) for k, v in l.items()}})
+        if width == 2048:
+            table, _ = kernel_table(rm, lm, device, timer)
+        del rm, lm
+        torch.cuda.empty_cache()
+    launches = _lib_seq.load().umbs_launch_count() + _lib.launch_count() - launches0
+    head = sizes[-1]["radanex_bf16"]
+    line = {"metric": "decode tokens/sec at batch 64 (Radanex bf16, width 2048, 8 layers, synthetic weights)",
+            "value": head["decode_b64_tok_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic", "vs_baseline": None, "gpu_launches": int(launches),
+            "config": {"name": "radanex", "workload": "prefill 1 x 2048 and 4 x 2048 tokens; decode at batch 1 / 8 / 64 behind a "
+                       "512-token context; Llama fp16 of the same width, depth and active feed-forward size beside it",
+                       "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": how},
+                       "l2": "whole-model runs stream more than L2 per step; kernel table flushes L2 between runs"},
+            "sizes": sizes, "kernels": table}
+    print(json.dumps(line))
