@@ -65,7 +65,7 @@ SIGNATURES = {
     "umbs_latent_norm": (c_int, [c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                  c_void_p]),
     "umbs_latent_attention": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, _BP, c_int, c_int, c_int, c_float,
-                                      c_void_p, c_void_p]),
+                                      c_void_p, c_size_t, c_void_p, c_void_p]),
     "umbs_ring_append": (c_int, [c_int, c_void_p, c_void_p, c_int, _BP, c_int, c_void_p]),
     "umbs_moe_route": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_void_p, c_void_p]),

@@ -35,6 +35,8 @@ struct Scratch {
     void* q;           // act [T, max heads dim]
     float* q_abs;      // fp32 [T, max heads kv_rank]
     void* o_lat;       // act [T, max heads kv_rank]
+    float* la_part;    // fp32 [min(T, 64), max heads, 8, max kv_rank + 2]  key-split partial states of decode steps
+    size_t la_part_bytes;
     float* mix_out;    // fp32 [T, width]
     float* sel_w;      // fp32 [T, max top]
     int32_t* grp_off;  // [max experts + 1]
@@ -50,7 +52,7 @@ struct Scratch {
 
 static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratch* s) {
     const size_t es = m->dtype == UMBS_F32 ? 4 : 2;
-    int rotd = 1, in_rows = 1, hv = 1, qr = 1, kvr = 1, hd = 1, hkv = 1, top = 1, experts = 1, ff = 1, sff = 1;
+    int hmax = 1, rotd = 1, in_rows = 1, hv = 1, qr = 1, kvr = 1, hd = 1, hkv = 1, top = 1, experts = 1, ff = 1, sff = 1;
     for (int i = 0; i < m->n_layers; ++i) {
         const umbs_layer_t& l = m->layers[i];
         auto up = [](int& a, int b) { if (b > a) a = b; };
@@ -58,7 +60,7 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
         if (l.mixer == UMBS_MIX_RETENTION) { up(in_rows, 2 * l.heads * l.dim + 2 * l.heads * l.vdim); up(rotd, l.rot_dims); }
         else {
             up(in_rows, l.q_rank + l.kv_rank);
-            up(qr, l.q_rank); up(kvr, l.kv_rank); up(hd, l.heads * l.dim); up(hkv, l.heads * l.kv_rank);
+            up(hmax, l.heads); up(qr, l.q_rank); up(kvr, l.kv_rank); up(hd, l.heads * l.dim); up(hkv, l.heads * l.kv_rank);
         }
         if (l.has_mlp) { up(top, l.mlp.top); up(experts, l.mlp.experts); up(ff, l.mlp.ff); up(sff, l.mlp.shared_ff); }
     }
@@ -78,6 +80,8 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
     z.q = a.take(Tz * hd * es);
     z.q_abs = (float*)a.take(Tz * hkv * 4);
     z.o_lat = a.take(Tz * hkv * es);
+    z.la_part_bytes = (size_t)(T < 64 ? T : 64) * 8 * ((size_t)hkv + 2 * (size_t)hmax) * 4;
+    z.la_part = (float*)a.take(z.la_part_bytes);
     z.mix_out = (float*)a.take(Tz * W * 4);
     z.sel_w = (float*)a.take(Tz * top * 4);
     z.grp_off = (int32_t*)a.take((size_t)(experts + 1) * 4);
@@ -137,8 +141,8 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
             // q_abs[t, h, :] = W_uk[h]^T q[t, h, :]: scores against the cached latents need no per-key up-projection
             UMBS_TRY(umbs_gemm(dt, s.q, hd, l.dim, l.w_ukT, l.dim, (int64_t)R * l.dim, s.q_abs, (int64_t)l.heads * R, R, 1, T, R,
                                l.dim, l.heads, nullptr, nullptr, 0, 0.f, stream));
-            UMBS_TRY(umbs_latent_attention(dt, s.q_abs, s.c, l.ring, l.ring_len, b, l.heads, R, l.window, l.scale, s.o_lat,
-                                           stream));
+            UMBS_TRY(umbs_latent_attention(dt, s.q_abs, s.c, l.ring, l.ring_len, b, l.heads, R, l.window, l.scale, s.la_part,
+                                           s.la_part_bytes, s.o_lat, stream));
             UMBS_TRY(umbs_ring_append(dt, s.c, l.ring, l.ring_len, b, R, stream));
             UMBS_TRY(umbs_gemm(dt, s.o_lat, (int64_t)l.heads * R, R, l.w_uv, R, (int64_t)l.vdim * R, s.mixed, hv, l.vdim, 0, T,
                                l.vdim, R, l.heads, nullptr, nullptr, 0, 0.f, stream));

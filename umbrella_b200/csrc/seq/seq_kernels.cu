@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
+#include <algorithm>
 #include <stdint.h>
 
 #include "seq_internal.h"
@@ -299,7 +300,7 @@ template <typename T, int RPL>
 __global__ void __launch_bounds__(256) latent_attention_kernel(const float* __restrict__ q_abs, const T* __restrict__ c,
                                                                const T* __restrict__ ring, int ring_len, Batch b, int heads,
                                                                int R, int window, float scale, int rpb, int vec,
-                                                               T* __restrict__ out) {
+                                                               int nsplit, float* __restrict__ part, T* __restrict__ out) {
     extern __shared__ __align__(16) float sm[];
     const int RS = ((R + 3) & ~3) + 4;                 // row stride: 16-byte rows, lanes 4 banks apart
     float* qs = sm;                                    // [32][RS]
@@ -330,8 +331,14 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const float* __re
         for (int i = 0; i < RPL; ++i) acc[a][i] = 0.f;
     }
     const int pos_first = pos0 + row0 / heads, pos_last = pos0 + (min(row0 + kLaRows, nrows) - 1) / heads;
-    const int jlo = max(0, pos_first - window + 1);
-    for (int j0 = jlo; j0 <= pos_last; j0 += kLaKeys) {
+    int jlo = max(0, pos_first - window + 1), jhi = pos_last;
+    if (nsplit > 1) {
+        // this block's share of the key tiles; the partial softmax states are merged by latent_merge_kernel
+        const int tiles = (pos_last - jlo) / kLaKeys + 1, per = (tiles + nsplit - 1) / nsplit;
+        jhi = min(pos_last, jlo + (int)(blockIdx.z + 1) * per * kLaKeys - 1);
+        jlo += blockIdx.z * per * kLaKeys;
+    }
+    for (int j0 = jlo; j0 <= jhi; j0 += kLaKeys) {
         __syncthreads();                                // the previous tile (and, first time round, qs) is done with
         if (vec) {
             // 16-byte pieces, every thread's loads of the tile in flight together
@@ -405,6 +412,21 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const float* __re
             }
         }
     }
+    if (nsplit > 1) {
+#pragma unroll
+        for (int a = 0; a < kLaQH; ++a) {
+            const int row = row0 + warp * kLaQH + a;
+            if (row >= nrows) continue;
+            float* dst = part + (((int64_t)(start + row / heads) * heads + row % heads) * nsplit + blockIdx.z) * (R + 2);
+            if (lane == 0) { dst[0] = m[a]; dst[1] = l[a]; }
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) {
+                const int r = lane + 32 * i;
+                if (r < R) dst[2 + r] = acc[a][i];
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int a = 0; a < kLaQH; ++a) {
         const int row = row0 + warp * kLaQH + a;
@@ -419,6 +441,29 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const float* __re
     }
 }
 
+// Merge of the key-split partial states: one warp per (token, head) row.
+template <typename T>
+__global__ void latent_merge_kernel(const float* __restrict__ part, int rows, int nsplit, int R, T* __restrict__ out) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* p = part + (int64_t)row * nsplit * (R + 2);
+    float mx = -INFINITY;
+    for (int i = 0; i < nsplit; ++i) mx = fmaxf(mx, p[i * (R + 2)]);
+    float den = 0.f;
+    for (int i = 0; i < nsplit; ++i) {
+        const float mi = p[i * (R + 2)];
+        if (mi > -INFINITY) den += expf(mi - mx) * p[i * (R + 2) + 1];
+    }
+    for (int r = lane; r < R; r += 32) {
+        float v = 0.f;
+        for (int i = 0; i < nsplit; ++i) {
+            const float mi = p[i * (R + 2)];
+            if (mi > -INFINITY) v = fmaf(expf(mi - mx), p[i * (R + 2) + 2 + r], v);
+        }
+        out[(int64_t)row * R + r] = from_f32<T>(v / den);
+    }
+}
+
 template <typename T>
 __global__ void ring_append_kernel(const T* __restrict__ c, T* __restrict__ ring, int ring_len, Batch b, int R) {
     const int t = blockIdx.x, s = b.tok_seq[t], pos = b.tok_pos[t];
@@ -428,24 +473,26 @@ __global__ void ring_append_kernel(const T* __restrict__ c, T* __restrict__ ring
 }
 
 // ------------------------------------------------------------------------------------------------ routing
-// One warp per token: logits in fp32, `top` rounds of arg-max (lowest index wins a tie), softmax over the chosen.
+// One block per token: the warps share the experts' logits (fp32 dot products, eight loads in flight per lane), then
+// one thread does `top` rounds of arg-max (lowest index wins a tie) and the softmax over the chosen.
 template <typename T>
-__global__ void moe_router_kernel(const T* __restrict__ h, int n, int width, const float* __restrict__ wr, int experts,
-                                  int top, float* __restrict__ sel_w, int32_t* __restrict__ sel_e,
-                                  int32_t* __restrict__ counts) {
-    extern __shared__ float sm[];          // [warps][experts]
-    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + wib;
-    if (t >= n) return;
-    float* z = sm + (size_t)wib * experts;
-    for (int e = 0; e < experts; ++e) {
+__global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h, int n, int width, const float* __restrict__ wr,
+                                                         int experts, int top, float* __restrict__ sel_w,
+                                                         int32_t* __restrict__ sel_e, int32_t* __restrict__ counts) {
+    extern __shared__ float z[];           // [experts]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int t = blockIdx.x;
+    const T* hr = h + (int64_t)t * width;
+    for (int e = warp; e < experts; e += nw) {
+        const float* w = wr + (int64_t)e * width;
         float s = 0.f;
-        for (int k = lane; k < width; k += 32) s += to_f32(h[(int64_t)t * width + k]) * wr[(int64_t)e * width + k];
+#pragma unroll 8
+        for (int k = lane; k < width; k += 32) s = fmaf(to_f32(hr[k]), w[k], s);
         s = warp_sum(s);
         if (lane == 0) z[e] = s;
     }
-    __syncwarp();
-    if (lane == 0) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
         float zmax = 0.f, den = 0.f;
         for (int k = 0; k < top; ++k) {
             int best = 0;
@@ -615,11 +662,20 @@ extern "C" int umbs_latent_norm(int dtype, const float* x, int n, int q_rank, in
 
 template <typename T>
 static int launch_latent_attention(const float* q_abs, const void* c, const void* ring, int ring_len, const Batch& b,
-                                   int heads, int R, int window, float scale, void* out, cudaStream_t st) {
+                                   int heads, int R, int window, float scale, float* part, size_t part_bytes, void* out,
+                                   cudaStream_t st) {
     const int rpb = b.max_seq_len == 1 ? 8 : kLaRows;
+    // decode steps: few blocks and a long serial walk over the window -> split the keys over up to 8 blocks per row tile
+    int nsplit = 1;
+    if (b.max_seq_len == 1 && part != nullptr) {
+        const int blocks = ((heads + rpb - 1) / rpb) * b.n_seqs;
+        const int tiles = (std::min(window, ring_len + 1) + kLaKeys - 1) / kLaKeys;
+        nsplit = std::max(1, std::min(std::min(8, tiles / 2), 296 / std::max(blocks, 1)));
+        if ((size_t)b.n_tokens * heads * nsplit * (R + 2) * sizeof(float) > part_bytes) nsplit = 1;
+    }
     const int ep = 16 / (int)sizeof(T);
     const int vec = (R % ep == 0) && ((uintptr_t)c % 16 == 0) && ((uintptr_t)ring % 16 == 0);
-    const dim3 grid((b.max_seq_len * heads + rpb - 1) / rpb, b.n_seqs), block(256);
+    const dim3 grid((b.max_seq_len * heads + rpb - 1) / rpb, b.n_seqs, nsplit), block(256);
     const size_t smem = (size_t)2 * kLaRows * (((R + 3) & ~3) + 4) * sizeof(float);
 #define UMBS_LA(RPL)                                                                                                   \
     do {                                                                                                               \
@@ -631,7 +687,8 @@ static int launch_latent_attention(const float* q_abs, const void* c, const void
             set = smem;                                                                                                \
         }                                                                                                              \
         latent_attention_kernel<T, RPL><<<grid, block, smem, st>>>(q_abs, (const T*)c, (const T*)ring, ring_len, b,    \
-                                                                   heads, R, window, scale, rpb, vec, (T*)out);        \
+                                                                   heads, R, window, scale, rpb, vec, nsplit, part,    \
+                                                                   (T*)out);                                           \
     } while (0)
     if (R <= 32) UMBS_LA(1);
     else if (R <= 64) UMBS_LA(2);
@@ -640,17 +697,22 @@ static int launch_latent_attention(const float* q_abs, const void* c, const void
     else if (R <= 512) UMBS_LA(16);
     else return UMB_ERR_UNSUPPORTED;
 #undef UMBS_LA
+    if (nsplit > 1) {
+        const int rows = b.n_tokens * heads;
+        latent_merge_kernel<T><<<(rows + 3) / 4, 128, 0, st>>>(part, rows, nsplit, R, (T*)out);
+        count_launches(1);
+    }
     return 0;
 }
 
 extern "C" int umbs_latent_attention(int dtype, const float* q_abs, const void* c, const void* ring, int ring_len,
-                                     const umbs_batch_t* batch, int heads, int kv_rank, int window, float scale, void* out,
-                                     umbs_stream_t stream) {
+                                     const umbs_batch_t* batch, int heads, int kv_rank, int window, float scale,
+                                     float* split_scratch, size_t split_bytes, void* out, umbs_stream_t stream) {
     if (batch->n_tokens <= 0) return 0;
     if (window < 1 || ring_len < 1) return UMB_ERR_ARG;
     int rc = 0;
     UMBS_DISPATCH_T(dtype, rc = launch_latent_attention<T>(q_abs, c, ring, ring_len, *batch, heads, kv_rank, window, scale,
-                                                           out, (cudaStream_t)stream));
+                                                           split_scratch, split_bytes, out, (cudaStream_t)stream));
     if (rc) return rc;
     count_launches(1);
     return (int)cudaGetLastError();
@@ -677,8 +739,8 @@ extern "C" int umbs_moe_route(int dtype, const void* h, int n, int width, const 
     int32_t* sel_e = scratch + 2 * experts;    // [n top]
     cudaError_t e = cudaMemsetAsync(counts, 0, experts * sizeof(int32_t), st);
     if (e != cudaSuccess) return (int)e;
-    const int wpb = 4;
-    UMBS_DISPATCH_T(dtype, moe_router_kernel<T><<<(n + wpb - 1) / wpb, 32 * wpb, (size_t)wpb * experts * sizeof(float), st>>>(
+    const int rthreads = experts >= 8 ? 256 : 32 * experts;
+    UMBS_DISPATCH_T(dtype, moe_router_kernel<T><<<n, rthreads, (size_t)experts * sizeof(float), st>>>(
                                (const T*)h, n, width, w_router, experts, top, sel_w, sel_e, counts));
     moe_offsets_kernel<<<1, 32, 0, st>>>(counts, experts, grp_off, cursor);
     const int pairs = n * top;
