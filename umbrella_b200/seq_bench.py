@@ -133,8 +133,12 @@ def kernel_table(rm, lm, device, timer, T=4096):
     rw, lw = rm.weights[ri], rm.weights[li]
     rows = []
 
-    def add(name, ms, nbytes=0, flops=0, like=None):
+    fp32_peak = 148 * 128 * 2 * 1.965e-3            # TFLOP/s: 148 SMs x 128 fp32 FMA lanes at the maximum SM clock (nominal)
+
+    def add(name, ms, nbytes=0, flops=0, like=None, flops32=0):
         r = dict(kernel=name, ms=round(ms, 4))
+        if flops32:
+            r["fp32_tflops"], r["frac_of_fp32_fma_peak"] = round(flops32 / ms / 1e9, 2), round(flops32 / ms / 1e9 / fp32_peak, 3)
         if flops:
             r["tflops"], r["frac_of_bf16_peak"] = round(flops / ms / 1e9, 1), round(flops / ms / 1e9 / tflops, 3)
         if nbytes:
@@ -175,7 +179,7 @@ def kernel_table(rm, lm, device, timer, T=4096):
                                        sp.norm_eps, state, torch.bfloat16))
         sbytes = nseq * ret.heads * ret.dim * ret.vdim * 4 * 2
         add(f"retention: rotary + recurrence + unit norm + gate, fp32 ({tag})", ms,
-            nbytes=n * ld * 4 + n * ret.heads * ret.vdim * (4 + 4 + 2) + sbytes)
+            nbytes=n * ld * 4 + n * ret.heads * ret.vdim * (4 + 4 + 2) + sbytes, flops32=4 * n * ret.heads * ret.dim * ret.vdim)
         # latent attention
         R = lat.kv_rank
         qa = torch.randn(n, lat.heads * R, device=device)
@@ -184,7 +188,7 @@ def kernel_table(rm, lm, device, timer, T=4096):
         ms = timer(lambda: Q.latent_attention(qa, c, ring, batch, lat.heads, lat.window, lat.scale, append=False))
         keys = sum(min(p + 1, lat.window) for p in range(per)) * nseq if n == T else n * min(513, lat.window)
         add(f"latent attention, window {lat.window}, fp32 scores ({tag})", ms,
-            nbytes=n * lat.heads * R * (4 + 2) + (n * R * 2 if n == T else keys * R * 2), flops=4 * keys * lat.heads * R)
+            nbytes=n * lat.heads * R * (4 + 2) + (n * R * 2 if n == T else keys * R * 2), flops32=4 * keys * lat.heads * R)
         # residual + depth mix
         stack = torch.randn(len(sp.layers) + 1, n, W, device=device)
         mix = torch.randn(n, W, device=device)
