@@ -152,8 +152,8 @@ int umbs_latent_norm(int dtype, const float* x, int n, int q_rank, int kv_rank, 
  * q_abs: fp32 [n_tokens, heads, kv_rank] (queries already multiplied by the key up-projection); keys and values are the
  * latents themselves: c (this step's, `dtype` [n_tokens, kv_rank]) for j >= seq_pos0, the slot's ring for older ones.
  * out: `dtype` [n_tokens, heads, kv_rank].  split_scratch (optional, fp32): a decode step (one token per sequence) splits
- * each row's keys over up to 8 blocks and merges the partial softmax states; it needs n_tokens heads 8 (kv_rank + 2)
- * floats there and runs unsplit when it gets less. */
+ * each row's keys over n blocks (as many as fill the GPU, at most one per 32 keys) and merges the partial softmax states;
+ * it needs n_tokens heads n (kv_rank + 2) floats there and runs unsplit when it gets less. */
 int umbs_latent_attention(int dtype, const float* q_abs, const void* c, const void* ring, int ring_len,
                           const umbs_batch_t* batch, int heads, int kv_rank, int window, float scale,
                           float* split_scratch, size_t split_bytes, void* out, umbs_stream_t stream);

@@ -2,12 +2,12 @@
 
 TEST INFRASTRUCTURE ONLY.  Nothing under ``oracle/`` is product code: only
 ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s ``cpu_baseline`` /
-``--impl reference`` legs may import it, and there only as the checker or as
+``--impl reference`` legs may import it, and there only as the comparison value or as
 the timed CPU baseline -- never as the shipped path.  The product path
 (``umbrella_b200``) raises if its CUDA library is missing; it never falls back
 to anything in here.
 
-What is restated (all citations relative to /root/reference, UMbreLLa @ ff1ac17):
+What is restated (all citations relative to the reference project's root, UMbreLLa @ ff1ac17):
 
 * ``oracle.tree``       -- Sequoia growmaps, tree accept, KV gather, state advance
                            (umbrella/sequoia_utils.py:40-130,

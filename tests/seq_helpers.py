@@ -21,7 +21,7 @@ MIXED = dict(width=64, vocab=96, groups=2, eps=1e-5, layers=[
 ])
 # dimensions the bf16 tensor-core product takes (every K a multiple of 32)
 ALIGNED = dict(width=128, vocab=160, groups=1, eps=1e-6, layers=[
-    dict(RET, heads=2, dim=32, vdim=64, rot_dims=32, decay=[0.96875, 0.998046875], mlp=dict(MLP, ff=64, shared_ff=32, n_experts=4)),
+    dict(RET, heads=4, dim=32, vdim=32, rot_dims=16, decay=[0.875, 0.9375, 0.984375, 0.998046875], mlp=dict(MLP, ff=64, shared_ff=32, n_experts=4)),
     dict(LAT, heads=4, dim=32, vdim=32, q_rank=64, kv_rank=64, window=20, mlp=dict(MLP, ff=64, shared_ff=32, n_experts=4)),
 ])
 

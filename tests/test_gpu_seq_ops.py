@@ -53,9 +53,10 @@ def test_gemm_batched_over_heads(ops):
         assert H.rel_err(got, ref) < tol
 
 
+@pytest.mark.parametrize("n", [37, 90])                 # one-block routing of a small step / routing spread over blocks
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-def test_gemm_expert_sorted_rows_with_gated_activation(ops, dt):
-    n, W, E, top, ff, limit = 37, 64, 4, 2, 32, 0.7
+def test_gemm_expert_sorted_rows_with_gated_activation(ops, dt, n):
+    W, E, top, ff, limit = 64, 4, 2, 32, 0.7
     h = torch.randn(n, W, generator=g(7)).to(dt)
     router = torch.randn(E, W, generator=g(8))
     gu = (torch.randn(E, 2 * ff, W, generator=g(9)) * 0.3).to(dt)
@@ -75,6 +76,22 @@ def test_gemm_expert_sorted_rows_with_gated_activation(ops, dt):
             uu = torch.clamp(h[t].double() @ up.T, -limit, limit)
             ref = gg * torch.sigmoid(1.702 * gg) * (uu + 1)
             assert H.rel_err(y[p], ref) < (1e-5 if dt == torch.float32 else 1e-2)
+
+
+def test_routing_of_a_token_does_not_depend_on_the_step_size(ops):
+    # the same tokens routed alone (one block for the whole step) and inside a large step (a block per token): the same
+    # experts in the same order and bit-equal weights
+    W, E, top = 96, 12, 3
+    h = torch.randn(300, W, generator=g(21)).to(DEV)
+    router = torch.randn(E, W, generator=g(22)).to(DEV)
+    big_w, _, _, _, big_e = ops.moe_route(h, router, top)
+    for lo, hi in ((0, 1), (5, 13), (280, 300)):
+        w, off, tok, pos, e = ops.moe_route(h[lo:hi].contiguous(), router, top)
+        assert torch.equal(e, big_e[lo:hi]) and torch.equal(w, big_w[lo:hi])
+        # pairs of an expert are listed in token order
+        off = off.cpu().tolist()
+        for x in range(E):
+            assert tok[off[x]:off[x + 1]].cpu().tolist() == sorted(tok[off[x]:off[x + 1]].cpu().tolist())
 
 
 # ---------------------------------------------------------------------------------------------- norm + token shift

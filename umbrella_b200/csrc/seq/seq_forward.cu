@@ -35,7 +35,7 @@ struct Scratch {
     void* q;           // act [T, max heads dim]
     float* q_abs;      // fp32 [T, max heads kv_rank]
     void* o_lat;       // act [T, max heads kv_rank]
-    float* la_part;    // fp32 [min(T, 64), max heads, 8, max kv_rank + 2]  key-split partial states of decode steps
+    float* la_part;    // fp32 [512 (tokens x splits), max heads, max kv_rank + 2]  key-split partial states of decode steps
     size_t la_part_bytes;
     float* mix_out;    // fp32 [T, width]
     float* sel_w;      // fp32 [T, max top]
@@ -80,7 +80,7 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
     z.q = a.take(Tz * hd * es);
     z.q_abs = (float*)a.take(Tz * hkv * 4);
     z.o_lat = a.take(Tz * hkv * es);
-    z.la_part_bytes = (size_t)(T < 64 ? T : 64) * 8 * ((size_t)hkv + 2 * (size_t)hmax) * 4;
+    z.la_part_bytes = (size_t)512 * ((size_t)hkv + 2 * (size_t)hmax) * 4;      // tokens x splits <= 512
     z.la_part = (float*)a.take(z.la_part_bytes);
     z.mix_out = (float*)a.take(Tz * W * 4);
     z.sel_w = (float*)a.take(Tz * top * 4);

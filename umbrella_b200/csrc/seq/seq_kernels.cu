@@ -131,12 +131,12 @@ __global__ void rotary_table_kernel(const int32_t* __restrict__ tok_pos, const f
 // One block = (sequence, head, 32 value columns).  Lane = column; warp w keeps rows [w DPT, (w + 1) DPT) of the
 // column's state in registers for the whole step.  Tokens go in order, TB at a time: the block rotates their q and k
 // into shared memory, every warp advances its slice of the state through the TB tokens and leaves its part of each
-// output in shared memory, and the parts are added in warp order.
-constexpr int kRetTB = 8;
-template <int DPT>
+// output in shared memory, and the parts are added in warp order.  TB = 16 (8 for the widest heads, whose staging
+// registers would not fit): a round's serial walk then outlasts the latency of the next round's scattered loads.
+template <int DPT, int kRetTB>
 __global__ void retention_kernel(const float* __restrict__ qkvg, int64_t ld, Batch b, int heads, int dim, int vdim,
-                                 int rot_dims, const float* __restrict__ rot_tab, const float* __restrict__ decay,
-                                 float* __restrict__ state, float* __restrict__ o_out) {
+                                 int rot_dims, const float* __restrict__ rot_tab, const float* __restrict__ inv_freq,
+                                 const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ o_out) {
     extern __shared__ __align__(16) float sm[];
     const int DS = blockDim.y, dimP = DS * DPT, nthr = 32 * DS;
     float* qs = sm;                          // [TB][dimP]
@@ -172,12 +172,21 @@ __global__ void retention_kernel(const float* __restrict__ qkvg, int64_t ld, Bat
                 pq[e] = row[qoff + d];
                 pk[e] = row[koff + d];
                 if (d < rot_dims) {
-                    const float* cs = rot_tab + tok * rot_dims;
                     const int partner = d < half ? d + half : d - half, f = d < half ? d : d - half;
                     pq2[e] = row[qoff + partner];
                     pk2[e] = row[koff + partner];
-                    pc[e] = cs[f];
-                    ps[e] = d < half ? -cs[half + f] : cs[half + f];
+                    float cv, sv;
+                    if (rot_tab != nullptr) {
+                        const float* cs = rot_tab + tok * rot_dims;
+                        cv = cs[f];
+                        sv = cs[half + f];
+                    } else {                     // no table (a decode step): the same angle, cosine and sine, in place
+                        const float ang = (float)b.tok_pos[tok] * inv_freq[f];
+                        cv = cosf(ang);
+                        sv = sinf(ang);
+                    }
+                    pc[e] = cv;
+                    ps[e] = d < half ? -sv : sv;
                 }
             }
         }
@@ -307,7 +316,6 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const float* __re
     float* cs = sm + (size_t)kLaRows * RS;             // [32][RS]
     const int s = blockIdx.y;
     const int len = b.seq_len[s], start = b.seq_start[s], pos0 = b.seq_pos0[s], slot = b.seq_slot[s];
-    // rpb rows of the 32 are used: a decode step has few rows per sequence and spreads them over more blocks
     const int row0 = blockIdx.x * rpb, nrows = min(len * heads, row0 + rpb);
     if (row0 >= nrows) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -441,26 +449,36 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const float* __re
     }
 }
 
-// Merge of the key-split partial states: one warp per (token, head) row.
+// Merge of the key-split partial states: one block per (token, head) row.  The splits' weights exp(m_i - max) / sum
+// are worked out once into shared memory; then every thread owns latent components and adds the splits in order
+// (independent loads, so they overlap).
 template <typename T>
-__global__ void latent_merge_kernel(const float* __restrict__ part, int rows, int nsplit, int R, T* __restrict__ out) {
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= rows) return;
+__global__ void latent_merge_kernel(const float* __restrict__ part, int nsplit, int R, T* __restrict__ out) {
+    extern __shared__ float wgt[];         // [nsplit]
+    const int row = blockIdx.x;
     const float* p = part + (int64_t)row * nsplit * (R + 2);
-    float mx = -INFINITY;
-    for (int i = 0; i < nsplit; ++i) mx = fmaxf(mx, p[i * (R + 2)]);
-    float den = 0.f;
-    for (int i = 0; i < nsplit; ++i) {
-        const float mi = p[i * (R + 2)];
-        if (mi > -INFINITY) den += expf(mi - mx) * p[i * (R + 2) + 1];
-    }
-    for (int r = lane; r < R; r += 32) {
-        float v = 0.f;
-        for (int i = 0; i < nsplit; ++i) {
-            const float mi = p[i * (R + 2)];
-            if (mi > -INFINITY) v = fmaf(expf(mi - mx), p[i * (R + 2) + 2 + r], v);
+    if (threadIdx.x < 32) {
+        float mx = -INFINITY;
+        for (int i = threadIdx.x; i < nsplit; i += 32) mx = fmaxf(mx, p[(int64_t)i * (R + 2)]);
+        mx = warp_max(mx);
+        float den = 0.f;
+        for (int i = threadIdx.x; i < nsplit; i += 32) {
+            const float mi = p[(int64_t)i * (R + 2)];
+            const float e = mi > -INFINITY ? expf(mi - mx) : 0.f;
+            wgt[i] = e;
+            den += e * p[(int64_t)i * (R + 2) + 1];
         }
-        out[(int64_t)row * R + r] = from_f32<T>(v / den);
+        den = warp_sum(den);
+        __syncwarp();
+        const float inv = 1.f / den;
+        for (int i = threadIdx.x; i < nsplit; i += 32) wgt[i] *= inv;
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < R; r += blockDim.x) {
+        float v = 0.f;
+#pragma unroll 4
+        for (int i = 0; i < nsplit; ++i) v = fmaf(wgt[i], p[(int64_t)i * (R + 2) + 2 + r], v);
+        out[(int64_t)row * R + r] = from_f32<T>(v);
     }
 }
 
@@ -473,8 +491,38 @@ __global__ void ring_append_kernel(const T* __restrict__ c, T* __restrict__ ring
 }
 
 // ------------------------------------------------------------------------------------------------ routing
-// One block per token: the warps share the experts' logits (fp32 dot products, eight loads in flight per lane), then
-// one thread does `top` rounds of arg-max (lowest index wins a tie) and the softmax over the chosen.
+// A router logit: fp32 dot product of one token's activations with one expert's row, lanes striding over the width and
+// a shuffle tree at the end.  Both routing kernels below use this one function, so a token's logits -- and with them its
+// experts -- do not depend on which of the two ran.
+template <typename T>
+__device__ __forceinline__ float router_logit(const T* __restrict__ hr, const float* __restrict__ w, int width, int lane) {
+    float s = 0.f;
+#pragma unroll 8
+    for (int k = lane; k < width; k += 32) s = fmaf(to_f32(hr[k]), w[k], s);
+    return warp_sum(s);
+}
+
+// `top` rounds of arg-max over z (lowest index wins a tie; z is consumed) and the softmax over the chosen logits.
+__device__ __forceinline__ void route_choose(float* z, int experts, int top, float* __restrict__ w_out,
+                                             int32_t* __restrict__ e_out, int32_t* counts) {
+    float zmax = 0.f, den = 0.f;
+    for (int k = 0; k < top; ++k) {
+        int best = 0;
+        float bv = -INFINITY;
+        for (int e = 0; e < experts; ++e)
+            if (z[e] > bv) { bv = z[e]; best = e; }
+        if (k == 0) zmax = bv;
+        const float p = expf(bv - zmax);
+        e_out[k] = best;
+        w_out[k] = p;
+        den += p;
+        z[best] = -INFINITY;
+        atomicAdd(counts + best, 1);
+    }
+    for (int k = 0; k < top; ++k) w_out[k] /= den;
+}
+
+// One block per token: the warps share the experts' logits, then one thread chooses.
 template <typename T>
 __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h, int n, int width, const float* __restrict__ wr,
                                                          int experts, int top, float* __restrict__ sel_w,
@@ -484,31 +532,50 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ h
     const int t = blockIdx.x;
     const T* hr = h + (int64_t)t * width;
     for (int e = warp; e < experts; e += nw) {
-        const float* w = wr + (int64_t)e * width;
-        float s = 0.f;
-#pragma unroll 8
-        for (int k = lane; k < width; k += 32) s = fmaf(to_f32(hr[k]), w[k], s);
-        s = warp_sum(s);
+        const float s = router_logit(hr, wr + (int64_t)e * width, width, lane);
         if (lane == 0) z[e] = s;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        float zmax = 0.f, den = 0.f;
-        for (int k = 0; k < top; ++k) {
-            int best = 0;
-            float bv = -INFINITY;
-            for (int e = 0; e < experts; ++e)
-                if (z[e] > bv) { bv = z[e]; best = e; }
-            if (k == 0) zmax = bv;
-            const float p = expf(bv - zmax);
-            sel_e[(int64_t)t * top + k] = best;
-            sel_w[(int64_t)t * top + k] = p;
-            den += p;
-            z[best] = -INFINITY;
-            atomicAdd(counts + best, 1);
-        }
-        for (int k = 0; k < top; ++k) sel_w[(int64_t)t * top + k] /= den;
+    if (threadIdx.x == 0) route_choose(z, experts, top, sel_w + (int64_t)t * top, sel_e + (int64_t)t * top, counts);
+}
+
+// The whole routing of a small step (a decode step) in one block: logits of every (token, expert) pair, the choice per
+// token, the experts' offsets in the sorted pair list and the scatter of the pairs into it.  Pairs of one expert are
+// listed in token order (one thread walks each expert's list), so the layout is the same from run to run.
+template <typename T>
+__global__ void __launch_bounds__(1024) moe_route_small_kernel(const T* __restrict__ h, int n, int width,
+                                                              const float* __restrict__ wr, int experts, int top,
+                                                              float* __restrict__ sel_w, int32_t* __restrict__ sel_e,
+                                                              int32_t* __restrict__ grp_off, int32_t* __restrict__ pair_tok,
+                                                              int32_t* __restrict__ pair_pos) {
+    extern __shared__ float zs[];                    // [n][experts] logits, then [experts] counts, [n top] chosen experts
+    int32_t* counts = reinterpret_cast<int32_t*>(zs + n * experts);
+    int32_t* offs = counts + experts;                // [experts + 1]
+    int32_t* chosen = offs + experts + 1;            // [n top]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < experts; i += blockDim.x) counts[i] = 0;
+    for (int i = warp; i < n * experts; i += nw) {
+        const int t = i / experts, e = i - t * experts;
+        const float s = router_logit(h + (int64_t)t * width, wr + (int64_t)e * width, width, lane);
+        if (lane == 0) zs[i] = s;
     }
+    __syncthreads();
+    for (int t = threadIdx.x; t < n; t += blockDim.x)
+        route_choose(zs + t * experts, experts, top, sel_w + (int64_t)t * top, chosen + t * top, counts);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int s = 0;
+        for (int e = 0; e < experts; ++e) { offs[e] = s; grp_off[e] = s; s += counts[e]; }
+        offs[experts] = s;
+        grp_off[experts] = s;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        int p = offs[e];
+        for (int i = 0; i < n * top && p < offs[e + 1]; ++i)
+            if (chosen[i] == e) { pair_tok[p] = i / top; pair_pos[i] = p; ++p; }
+    }
+    for (int i = threadIdx.x; i < n * top; i += blockDim.x) sel_e[i] = chosen[i];
 }
 
 __global__ void moe_offsets_kernel(const int32_t* __restrict__ counts, int experts, int32_t* __restrict__ grp_off,
@@ -610,19 +677,21 @@ extern "C" int umbs_group_norm_rows(int dtype, const float* x, const int32_t* ro
     return (int)cudaGetLastError();
 }
 
-template <int DPT>
+template <int DPT, int kRetTB>
 static int launch_retention(const float* qkvg, int64_t ld, const Batch& b, int heads, int dim, int vdim, int rot_dims,
-                            const float* rot_tab, const float* decay, float* state, float* o, cudaStream_t st) {
+                            const float* rot_tab, const float* inv_freq, const float* decay, float* state, float* o,
+                            cudaStream_t st) {
     const int ds = (dim + DPT - 1) / DPT;
     const dim3 grid(b.n_seqs, heads, (vdim + 31) / 32), block(32, ds);
     const size_t smem = ((size_t)2 * kRetTB * ds * DPT + (size_t)ds * kRetTB * 32 + kRetTB * 32) * sizeof(float);
     static size_t set = 0;
     if (smem > 48 * 1024 && smem > set) {
-        cudaError_t e = cudaFuncSetAttribute(retention_kernel<DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(retention_kernel<DPT, kRetTB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         set = smem;
     }
-    retention_kernel<DPT><<<grid, block, smem, st>>>(qkvg, ld, b, heads, dim, vdim, rot_dims, rot_tab, decay, state, o);
+    retention_kernel<DPT, kRetTB><<<grid, block, smem, st>>>(qkvg, ld, b, heads, dim, vdim, rot_dims, rot_tab, inv_freq, decay,
+                                                             state, o);
     return 0;
 }
 
@@ -633,14 +702,18 @@ extern "C" int umbs_retention(int dtype, const float* qkvg, int64_t ld, const um
     if (rot_dims < 0 || rot_dims > dim || (rot_dims & 1)) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     unsigned launches = 2;
-    if (rot_dims > 0) {
+    // a step with several tokens per sequence shares one cos | sin table between heads and column blocks; a decode step
+    // works the few values out inside the recurrence kernel
+    const float* rot_tab = nullptr;
+    if (rot_dims > 0 && batch->max_seq_len > 1) {
         rotary_table_kernel<<<batch->n_tokens, 64, 0, st>>>(batch->tok_pos, inv_freq, rot_dims / 2, rot_scratch);
+        rot_tab = rot_scratch;
         ++launches;
     }
     int rc;
-    if (dim <= 32) rc = launch_retention<8>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_scratch, decay, state, o_scratch, st);
-    else if (dim <= 128) rc = launch_retention<16>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_scratch, decay, state, o_scratch, st);
-    else if (dim <= 512) rc = launch_retention<32>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_scratch, decay, state, o_scratch, st);
+    if (dim <= 32) rc = launch_retention<8, 16>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_tab, inv_freq, decay, state, o_scratch, st);
+    else if (dim <= 128) rc = launch_retention<16, 16>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_tab, inv_freq, decay, state, o_scratch, st);
+    else if (dim <= 512) rc = launch_retention<32, 8>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_tab, inv_freq, decay, state, o_scratch, st);
     else return UMB_ERR_UNSUPPORTED;
     if (rc) return rc;
     const int warps = batch->n_tokens * heads;
@@ -664,19 +737,22 @@ template <typename T>
 static int launch_latent_attention(const float* q_abs, const void* c, const void* ring, int ring_len, const Batch& b,
                                    int heads, int R, int window, float scale, float* part, size_t part_bytes, void* out,
                                    cudaStream_t st) {
-    const int rpb = b.max_seq_len == 1 ? 8 : kLaRows;
-    // decode steps: few blocks and a long serial walk over the window -> split the keys over up to 8 blocks per row tile
+    const int rpb = kLaRows;
+    const size_t smem = (size_t)2 * kLaRows * (((R + 3) & ~3) + 4) * sizeof(float);
+    // decode steps: few blocks and a long serial walk over the window -> split the keys over as many blocks per row tile
+    // as fill the GPU (as many block slots per SM as the tiles' shared memory allows), as far as the scratch buffer reaches
     int nsplit = 1;
     if (b.max_seq_len == 1 && part != nullptr) {
         const int blocks = ((heads + rpb - 1) / rpb) * b.n_seqs;
         const int tiles = (std::min(window, ring_len + 1) + kLaKeys - 1) / kLaKeys;
-        nsplit = std::max(1, std::min(std::min(8, tiles / 2), 296 / std::max(blocks, 1)));
-        if ((size_t)b.n_tokens * heads * nsplit * (R + 2) * sizeof(float) > part_bytes) nsplit = 1;
+        const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(4, (size_t)227 * 1024 / (smem + 1024)));
+        nsplit = std::max(1, std::min(tiles, 148 * per_sm / std::max(blocks, 1)));   // down to one key tile per block
+        const size_t fit = part_bytes / ((size_t)b.n_tokens * heads * (R + 2) * sizeof(float));   // splits the scratch holds
+        nsplit = (int)std::max<size_t>(1, std::min<size_t>(nsplit, fit));
     }
     const int ep = 16 / (int)sizeof(T);
     const int vec = (R % ep == 0) && ((uintptr_t)c % 16 == 0) && ((uintptr_t)ring % 16 == 0);
     const dim3 grid((b.max_seq_len * heads + rpb - 1) / rpb, b.n_seqs, nsplit), block(256);
-    const size_t smem = (size_t)2 * kLaRows * (((R + 3) & ~3) + 4) * sizeof(float);
 #define UMBS_LA(RPL)                                                                                                   \
     do {                                                                                                               \
         static size_t set = 0;                                                                                         \
@@ -699,7 +775,7 @@ static int launch_latent_attention(const float* q_abs, const void* c, const void
 #undef UMBS_LA
     if (nsplit > 1) {
         const int rows = b.n_tokens * heads;
-        latent_merge_kernel<T><<<(rows + 3) / 4, 128, 0, st>>>(part, rows, nsplit, R, (T*)out);
+        latent_merge_kernel<T><<<rows, R >= 256 ? 256 : (R >= 128 ? 128 : 64), nsplit * sizeof(float), st>>>(part, nsplit, R, (T*)out);
         count_launches(1);
     }
     return 0;
@@ -734,6 +810,15 @@ extern "C" int umbs_moe_route(int dtype, const void* h, int n, int width, const 
     if (n <= 0) return 0;
     if (top < 1 || top > experts) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
+    if ((size_t)n * experts <= 256 && (size_t)n * top <= 1024) {
+        // a small step (decoding): one block does the logits, the choice, the offsets and the sorted pair list
+        const size_t smem = ((size_t)n * experts + 2 * (size_t)experts + 1 + (size_t)n * top) * sizeof(float);
+        UMBS_DISPATCH_T(dtype, moe_route_small_kernel<T><<<1, 1024, smem, st>>>((const T*)h, n, width, w_router, experts, top,
+                                                                              sel_w, scratch + 2 * experts, grp_off, pair_tok,
+                                                                              pair_pos));
+        count_launches(1);
+        return (int)cudaGetLastError();
+    }
     int32_t* counts = scratch;                 // [experts]
     int32_t* cursor = scratch + experts;       // [experts]
     int32_t* sel_e = scratch + 2 * experts;    // [n top]

@@ -100,7 +100,7 @@ def latent_attention(q_abs, c, ring, batch: RaggedBatch, heads, window, scale, a
     T, R = c.shape
     out = torch.empty((T, heads * R), dtype=c.dtype, device=c.device)
     lib = S.load()
-    part = torch.empty(T * heads * 8 * (R + 2), dtype=torch.float32, device=c.device) if T <= 64 else None
+    part = torch.empty(512 * heads * (R + 2), dtype=torch.float32, device=c.device) if T <= 64 else None
     S.check(lib.umbs_latent_attention(_mode(c), _p(q_abs), _p(c), _p(ring), ring.shape[1], C.byref(batch.c), heads, R, window,
                                       float(scale), _p(part), part.numel() * 4 if part is not None else 0, _p(out), _stream()),
             "latent_attention")

@@ -13,7 +13,7 @@ joins a running batch.
 state slots (allocating one for an id it has not seen), runs ``model.forward`` and releases the slots of finished
 requests.  Sampling is the framework's fused sampler (ops.sample: arg-max, or top-k / top-p at a temperature).
 
-Engine-contract methods that only make sense with a draft model (``build_tree``) are no-ops here; ``verify`` is one
+Engine-interface methods that only make sense with a draft model (``build_tree``) are no-ops here; ``verify`` is one
 decoding step of the single interactive sequence.
 """
 from __future__ import annotations
@@ -155,7 +155,7 @@ class BatchDecodingEngine(BaseEngine):
         out = self.run_queue()
         return [out[("gen", i)] for i in range(len(prompts))]
 
-    # ------------------------------------------------------------------ single-sequence surface of the contract
+    # ------------------------------------------------------------------ single-sequence surface of the engine interface
     def _encode(self, text):
         if self.tokenizer is None:
             raise RuntimeError("no tokenizer: pass token ids (input_ids=...)")
