@@ -48,15 +48,38 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __res
 }
 
 // ------------------------------------------------------------------------------------------------ group norm (+ shift)
-// inverse root mean square of group g of row x (all threads get it)
-__device__ float group_inv_rms(const float* __restrict__ x, int g, int gsz, float eps, float* red) {
-    float s = 0.f;
-    for (int e = threadIdx.x; e < gsz; e += blockDim.x) {
-        const float v = x[g * gsz + e];
-        s += v * v;
+// Inverse root mean square of every group of row xr (and of row xp, if given), for all threads of the block.  Each
+// group's sum of squares is split over blockDim / 32 / groups warps (at least one), all groups at once, so the row's loads
+// are in flight together and the block synchronises twice whatever the number of groups.  The order of the additions
+// depends on the block size only.  part: 2 groups max(1, warps / groups)
+// floats of shared memory.
+__device__ void group_inv_rms_all(const float* __restrict__ xr, const float* __restrict__ xp, int width, int groups, float eps,
+                                  float* part, float* inv_own, float* inv_prev) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int gsz = width / groups, wpg = max(1, nw / groups), slots = groups * wpg;
+    for (int slot = warp; slot < slots; slot += nw) {
+        const int g = slot / wpg, pt = slot - g * wpg;
+        float a = 0.f, b = 0.f;
+        for (int e = pt * 32 + lane; e < gsz; e += wpg * 32) {
+            const float v = xr[g * gsz + e];
+            a = fmaf(v, v, a);
+            if (xp != nullptr) {
+                const float u = xp[g * gsz + e];
+                b = fmaf(u, u, b);
+            }
+        }
+        a = warp_sum(a);
+        b = warp_sum(b);
+        if (lane == 0) { part[slot] = a; part[slots + slot] = b; }
     }
-    s = block_sum(s, red);
-    return 1.f / sqrtf(s / (float)gsz + eps);
+    __syncthreads();
+    for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+        float a = 0.f, b = 0.f;
+        for (int pt = 0; pt < wpg; ++pt) { a += part[g * wpg + pt]; b += part[slots + g * wpg + pt]; }
+        inv_own[g] = 1.f / sqrtf(a / (float)gsz + eps);
+        if (inv_prev != nullptr) inv_prev[g] = xp != nullptr ? 1.f / sqrtf(b / (float)gsz + eps) : 0.f;
+    }
+    __syncthreads();
 }
 
 template <typename T>
@@ -64,23 +87,17 @@ __global__ void group_norm_shift_kernel(const float* __restrict__ x, const float
                                         const float* __restrict__ shift_w, float* __restrict__ shift_state, int slots,
                                         Batch b, int width, int groups, float eps, T* __restrict__ h_out,
                                         T* __restrict__ hs_out) {
-    extern __shared__ float sm[];     // [groups] own inverse rms, [groups] previous token's, [33] reduction
+    extern __shared__ float sm[];     // [groups] own inverse rms, [groups] previous token's, partial sums
     float* inv_own = sm;
     float* inv_prev = sm + groups;
-    float* red = sm + 2 * groups;
+    float* part = sm + 2 * groups;
     const int t = blockIdx.x, s = b.tok_seq[t];
     const int start = b.seq_start[s], len = b.seq_len[s], pos0 = b.seq_pos0[s], slot = b.seq_slot[s], par = b.seq_parity[s];
     const int gsz = width / groups;
     const bool first = (t == start), last = (t == start + len - 1);
     const float* xr = x + (int64_t)t * width;
     const float* xp = xr - width;
-    for (int g = 0; g < groups; ++g) {
-        const float a = group_inv_rms(xr, g, gsz, eps, red);
-        float p = 0.f;
-        if (shift_w != nullptr && !first) p = group_inv_rms(xp, g, gsz, eps, red);
-        if (threadIdx.x == 0) { inv_own[g] = a; inv_prev[g] = p; }
-    }
-    __syncthreads();
+    group_inv_rms_all(xr, (shift_w != nullptr && !first) ? xp : nullptr, width, groups, eps, part, inv_own, inv_prev);
     const float* st_in = shift_state + ((int64_t)par * slots + slot) * width;
     float* st_out = shift_state + ((int64_t)(par ^ 1) * slots + slot) * width;
     for (int e = threadIdx.x; e < width; e += blockDim.x) {
@@ -102,15 +119,11 @@ __global__ void group_norm_rows_kernel(const float* __restrict__ x, const int32_
                                        const float* __restrict__ w, int width, int groups, float eps, T* __restrict__ y) {
     extern __shared__ float sm[];
     float* inv = sm;
-    float* red = sm + groups;
+    float* part = sm + groups;
     const int r = blockIdx.x;
     const float* xr = x + (int64_t)(rows ? rows[r] : r) * width;
     const int gsz = width / groups;
-    for (int g = 0; g < groups; ++g) {
-        const float a = group_inv_rms(xr, g, gsz, eps, red);
-        if (threadIdx.x == 0) inv[g] = a;
-    }
-    __syncthreads();
+    group_inv_rms_all(xr, nullptr, width, groups, eps, part, inv, nullptr);
     for (int e = threadIdx.x; e < width; e += blockDim.x)
         y[(int64_t)r * width + e] = from_f32<T>(xr[e] * inv[e / gsz] * w[e]);
 }
@@ -658,8 +671,9 @@ extern "C" int umbs_group_norm_shift(int dtype, const float* x, const float* w, 
     if (batch->n_tokens <= 0) return 0;
     if (groups <= 0 || width % groups != 0) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    const size_t smem = (2 * groups + 33) * sizeof(float);
-    UMBS_DISPATCH_T(dtype, group_norm_shift_kernel<T><<<batch->n_tokens, threads_for(width / groups), smem, st>>>(
+    const int threads = threads_for(width);
+    const size_t smem = (2 * (size_t)groups + 2 * (size_t)groups * std::max(1, threads / 32 / groups)) * sizeof(float);
+    UMBS_DISPATCH_T(dtype, group_norm_shift_kernel<T><<<batch->n_tokens, threads, smem, st>>>(
                                x, w, shift_w, shift_state, slots, *batch, width, groups, eps, (T*)h, (T*)hs));
     count_launches(1);
     return (int)cudaGetLastError();
@@ -670,8 +684,9 @@ extern "C" int umbs_group_norm_rows(int dtype, const float* x, const int32_t* ro
     if (n_rows <= 0) return 0;
     if (groups <= 0 || width % groups != 0) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    const size_t smem = (groups + 33) * sizeof(float);
-    UMBS_DISPATCH_T(dtype, group_norm_rows_kernel<T><<<n_rows, threads_for(width / groups), smem, st>>>(
+    const int threads = threads_for(width);
+    const size_t smem = ((size_t)groups + 2 * (size_t)groups * std::max(1, threads / 32 / groups)) * sizeof(float);
+    UMBS_DISPATCH_T(dtype, group_norm_rows_kernel<T><<<n_rows, threads, smem, st>>>(
                                x, rows, w, width, groups, eps, (T*)y));
     count_launches(1);
     return (int)cudaGetLastError();
