@@ -461,6 +461,11 @@ def test_packaged_configs_build_engines():
     assert len(files) >= 5
     for f in files:
         cfg = json.load(open(f))
+        if cfg["engine"] == "batch":                           # sequence-state decoders: no draft model, no tree
+            eng = AutoEngine.from_config("cuda:0", **cfg)
+            assert type(eng).__name__ == "BatchDecodingEngine" and "draft_model" not in cfg
+            assert eng.temperature == cfg["temperature"]
+            continue
         assert KNOWN_MODELS.get(cfg["model"]) and KNOWN_MODELS.get(cfg["draft_model"]), f
         eng = AutoEngine.from_config("cuda:0", **cfg)          # construction is host-only; initialize() needs the GPU
         assert type(eng).__name__ == {"static": "StaticSpeculationEngine", "dynamic": "DynamicSpeculationEngine"}[cfg["engine"]]
