@@ -49,6 +49,7 @@ typedef struct {
     const int32_t* seq_pos0;  /* [n_seqs] position of its first token (0 = a fresh sequence: state read as zero) */
     const int32_t* seq_parity;/* [n_seqs] */
     const int32_t* want_rows; /* [n_want] tokens whose logits are wanted */
+    int max_pos0;             /* host copy of the largest seq_pos0: 0 = every sequence of the step is fresh */
 } umbs_batch_t;
 
 /* Gated feed-forward block: y = W_down( act(W_gate h, W_up h) ), act(g, u) = g' sigmoid(1.702 g') (u' + 1) with
@@ -81,6 +82,8 @@ typedef struct {
     const void* w_uq;          /* [heads dim, q_rank] */
     const void* w_ukT;         /* [heads, kv_rank, dim]: the key up-projection, transposed per head */
     const void* w_uv;          /* [heads vdim, kv_rank] */
+    const void* w_ukv;         /* [heads dim + heads vdim, kv_rank]: key rows then value rows, or NULL; with it a step of
+                                * fresh sequences up-projects its latents once and attends over per-head keys */
     void* ring;                /* act dtype [slots, ring_len, kv_rank] */
     /* both */
     const void* w_in;          /* retention: [q | k | v | g] rows; latent attention: [dq | dkv] rows; [., width] */
@@ -157,6 +160,15 @@ int umbs_latent_norm(int dtype, const float* x, int n, int q_rank, int kv_rank, 
 int umbs_latent_attention(int dtype, const float* q_abs, const void* c, const void* ring, int ring_len,
                           const umbs_batch_t* batch, int heads, int kv_rank, int window, float scale,
                           float* split_scratch, size_t split_bytes, void* out, umbs_stream_t stream);
+
+/* Sliding-window softmax attention of a step whose keys all sit in the step (fresh sequences): q, k [n_tokens, heads,
+ * dim] and v [n_tokens, heads, vdim] in `dtype` with row strides ldq / ldk / ldv (elements); row i of a sequence sees
+ * rows j of the same sequence with 0 <= i - j < window.  fp32 scores and softmax.  out: `dtype`, row stride ldo, heads
+ * side by side.  dim and vdim up to 128 (umbs_window_attention_fits), else UMB_ERR_UNSUPPORTED. */
+int umbs_window_attention_fits(int dim, int vdim);
+int umbs_window_attention(int dtype, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
+                          const umbs_batch_t* batch, int heads, int dim, int vdim, int window, float scale, void* out,
+                          int64_t ldo, umbs_stream_t stream);
 
 /* Stores this step's latents into the slots' rings (position p at row p mod ring_len). */
 int umbs_ring_append(int dtype, const void* c, void* ring, int ring_len, const umbs_batch_t* batch, int kv_rank,

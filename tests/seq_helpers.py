@@ -115,12 +115,12 @@ def write_checkpoint(path, cfg, t):
     return path
 
 
-def product_model(cfg, t, dtype=torch.float32, device="cuda:0", slots=4, tmp=None):
+def product_model(cfg, t, dtype=torch.float32, device="cuda:0", slots=4, tmp=None, **kw):
     """The product model over the same tensors, through the family's config reader and checkpoint loader."""
     import tempfile
     from umbrella_b200.models.auto_model import AutoModelLM
     d = write_checkpoint(tmp or tempfile.mkdtemp(prefix="seqckpt"), cfg, t)
-    m = AutoModelLM.from_pretrained(d, device=device, dtype=dtype, slots=slots)
+    m = AutoModelLM.from_pretrained(d, device=device, dtype=dtype, slots=slots, **kw)
     m.alloc()
     return m
 

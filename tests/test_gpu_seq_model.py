@@ -51,6 +51,25 @@ def test_whole_prompt_and_layers(mixed):
     assert H.row_err(got, ref) < TOL32
 
 
+def test_whole_prompt_over_latents_and_over_per_head_keys():
+    """A whole prompt's latent attention runs over keys and values up-projected once per token; with that switched off it
+    runs over the latents, as later portions and decode steps do.  Both are the oracle's numbers, also in one batch."""
+    cfg = dict(H.MIXED, layers=[dict(H.LAT, window=40, heads=3, dim=24, vdim=40, mlp=H.MLP), dict(H.RET, mlp=None),
+                                dict(H.LAT, window=100, mlp=None)])
+    t = H.random_tensors(cfg, seed=12)
+    om = H.oracle_model(cfg, t)
+    seqs = [toks(n, cfg["vocab"], 40 + n) for n in (130, 1, 66)]
+    refs = [O.forward(om, s) for s in seqs]
+    for fresh in (True, False):
+        pm = H.product_model(cfg, t, torch.float32, fresh_attention=fresh)
+        slots = [pm.cache.alloc_slot() for _ in seqs]
+        got = pm.forward([(slots[i], s, range(len(s))) for i, s in enumerate(seqs)])
+        assert H.row_err(got, torch.cat(refs)) < TOL32, fresh
+        nxt = pm.forward([(slots[0], [5], [0]), (slots[2], [7], [0])])           # decoding goes on from the ring either way
+        assert H.row_err(nxt[0:1], O.forward(om, seqs[0] + [5])[-1:]) < TOL32
+        assert H.row_err(nxt[1:2], O.forward(om, seqs[2] + [7])[-1:]) < TOL32
+
+
 def test_first_tokens(mixed):
     cfg, om, pm = mixed
     for n in (1, 2, 3):

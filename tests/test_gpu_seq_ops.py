@@ -222,6 +222,52 @@ def test_latent_attention_window_edge(ops, decode):
     assert H.row_err(out, _lat_ref(q_abs, c, 1.0, window)) < 2e-5
 
 
+# ---------------------------------------------------------------------------------------------- attention among a step's own tokens
+@pytest.mark.parametrize("dt,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("Hh,D,V,window", [(3, 24, 40, 7), (2, 16, 96, 70), (1, 72, 8, 1), (2, 32, 64, 200)])
+def test_window_attention_whole_and_batch(ops, dt, tol, Hh, D, V, window):
+    lens = [150, 1, 64, 65, 3]                                      # over two row tiles, a single token, exactly one tile, one more
+    n = sum(lens)
+    q = torch.randn(n, Hh, D, generator=g(31)).to(dt)
+    kv = torch.randn(n, Hh * (D + V), generator=g(32)).to(dt)       # keys | values side by side, as the step lays them out
+    k, v = kv[:, :Hh * D].reshape(n, Hh, D), kv[:, Hh * D:].reshape(n, Hh, V)
+    refs, at = [], 0
+    for m in lens:
+        refs.append(O.windowed_softmax_attention(q[at:at + m].double(), k[at:at + m].double(), v[at:at + m].double(), 0.3, window))
+        at += m
+    ref = torch.cat(refs).reshape(n, Hh * V)
+    starts = [sum(lens[:i]) for i in range(len(lens))]
+    kvd = kv.to(DEV)
+    got = ops.window_attention(q.reshape(n, Hh * D).to(DEV), kvd[:, :Hh * D], kvd[:, Hh * D:],
+                               ops.RaggedBatch([(i, m, 0, 0) for i, m in enumerate(lens)], DEV), Hh, window, 0.3)
+    assert H.row_err(got, ref) < tol
+    for i in (0, 3):                                                # each request alone: the same rows
+        m, a = lens[i], starts[i]
+        alone = ops.window_attention(q[a:a + m].reshape(m, Hh * D).to(DEV).contiguous(), kvd[a:a + m, :Hh * D], kvd[a:a + m, Hh * D:],
+                                     ops.RaggedBatch([(0, m, 0, 0)], DEV), Hh, window, 0.3)
+        assert torch.equal(alone, got[a:a + m])
+
+
+def test_window_attention_edge_and_tile_border(ops):
+    """One key stands out.  The last row that sees it returns its value, the next row does not; the key sits so that the
+    edge falls on the border between two key tiles, and once just behind it."""
+    D, V, n = 16, 8, 200
+    for key, window in ((1, 63), (1, 64), (60, 70), (127, 2)):
+        k = torch.randn(n, 1, D, generator=g(33)) * 0.05
+        v = torch.randn(n, 1, V, generator=g(34)) * 0.05
+        k[key] = 0.0
+        k[key, 0, 5] = 6.0
+        v[key, 0, 2] = 9.0
+        q = torch.zeros(n, 1, D)
+        q[:, 0, 5] = 8.0
+        got = ops.window_attention(q.reshape(n, D).to(DEV), k.reshape(n, D).to(DEV), v.reshape(n, V).to(DEV),
+                                   ops.RaggedBatch([(0, n, 0, 0)], DEV), 1, window, 1.0).cpu()
+        inside, outside = key + window - 1, key + window
+        assert got[inside, 2] > 8.9 and got[key, 2] > 8.9, (key, window)
+        assert abs(got[outside, 2]) < 0.5 and abs(got[key - 1, 2]) < 0.5, (key, window)
+        assert H.row_err(got, O.windowed_softmax_attention(q.double(), k.double(), v.double(), 1.0, window).reshape(n, V)) < 2e-5
+
+
 # ---------------------------------------------------------------------------------------------- residual + depth mix
 def test_depth_mix(ops):
     n, W, L = 9, 40, 3

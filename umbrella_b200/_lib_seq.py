@@ -1,7 +1,7 @@
 """ctypes binding of libumbrella_b200_seq.so (the C ABI declared in include/umbrella_b200_seq.h): the batched step
 of the sequence-state decoders and its building blocks.
 
-The library is compiled in-tree on first use when it is missing or older than its sources (``build.build_seq``: three
+The library is compiled in-tree on first use when it is missing or older than its sources (``build.build_seq``: four
 small translation units, seconds) -- a fresh checkout serves these models without a separate build step.  There is
 no PyTorch / CPU fallback behind these calls: without nvcc and without the library, loading is an error.
 """
@@ -23,7 +23,7 @@ class Batch(C.Structure):
     _fields_ = [("n_tokens", c_int), ("n_seqs", c_int), ("n_want", c_int), ("max_seq_len", c_int),
                 ("tok_ids", c_void_p), ("tok_seq", c_void_p), ("tok_pos", c_void_p), ("seq_slot", c_void_p),
                 ("seq_start", c_void_p), ("seq_len", c_void_p), ("seq_pos0", c_void_p), ("seq_parity", c_void_p),
-                ("want_rows", c_void_p)]
+                ("want_rows", c_void_p), ("max_pos0", c_int)]
 
 
 class Mlp(C.Structure):
@@ -37,7 +37,7 @@ class Layer(C.Structure):
                 ("rot_dims", c_int), ("inv_freq", c_void_p), ("decay", c_void_p), ("ret_state", c_void_p),
                 ("q_rank", c_int), ("kv_rank", c_int), ("window", c_int), ("ring_len", c_int), ("scale", c_float),
                 ("q_norm", c_void_p), ("kv_norm", c_void_p), ("w_uq", c_void_p), ("w_ukT", c_void_p), ("w_uv", c_void_p),
-                ("ring", c_void_p),
+                ("w_ukv", c_void_p), ("ring", c_void_p),
                 ("w_in", c_void_p), ("w_o", c_void_p), ("norm_w", c_void_p), ("shift_w", c_void_p),
                 ("shift_state", c_void_p), ("depth_w", c_void_p), ("has_mlp", c_int), ("mlp", Mlp)]
 
@@ -66,6 +66,9 @@ SIGNATURES = {
                                  c_void_p]),
     "umbs_latent_attention": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, _BP, c_int, c_int, c_int, c_float,
                                       c_void_p, c_size_t, c_void_p, c_void_p]),
+    "umbs_window_attention_fits": (c_int, [c_int, c_int]),
+    "umbs_window_attention": (c_int, [c_int, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, _BP, c_int, c_int,
+                                      c_int, c_int, c_float, c_void_p, c_int64, c_void_p]),
     "umbs_ring_append": (c_int, [c_int, c_void_p, c_void_p, c_int, _BP, c_int, c_void_p]),
     "umbs_moe_route": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_void_p, c_void_p]),

@@ -35,6 +35,7 @@ struct Scratch {
     void* q;           // act [T, max heads dim]
     float* q_abs;      // fp32 [T, max heads kv_rank]
     void* o_lat;       // act [T, max heads kv_rank]
+    void* kv;          // act [T, max heads (dim + vdim)]  per-head keys | values of a step of fresh sequences
     float* la_part;    // fp32 [512 (tokens x splits), max heads, max kv_rank + 2]  key-split partial states of decode steps
     size_t la_part_bytes;
     float* mix_out;    // fp32 [T, width]
@@ -52,7 +53,7 @@ struct Scratch {
 
 static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratch* s) {
     const size_t es = m->dtype == UMBS_F32 ? 4 : 2;
-    int hmax = 1, rotd = 1, in_rows = 1, hv = 1, qr = 1, kvr = 1, hd = 1, hkv = 1, top = 1, experts = 1, ff = 1, sff = 1;
+    int hmax = 1, rotd = 1, in_rows = 1, hv = 1, qr = 1, kvr = 1, hd = 1, hkv = 1, hkvw = 1, top = 1, experts = 1, ff = 1, sff = 1;
     for (int i = 0; i < m->n_layers; ++i) {
         const umbs_layer_t& l = m->layers[i];
         auto up = [](int& a, int b) { if (b > a) a = b; };
@@ -61,6 +62,7 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
         else {
             up(in_rows, l.q_rank + l.kv_rank);
             up(hmax, l.heads); up(qr, l.q_rank); up(kvr, l.kv_rank); up(hd, l.heads * l.dim); up(hkv, l.heads * l.kv_rank);
+            if (l.w_ukv != nullptr) up(hkvw, l.heads * (l.dim + l.vdim));
         }
         if (l.has_mlp) { up(top, l.mlp.top); up(experts, l.mlp.experts); up(ff, l.mlp.ff); up(sff, l.mlp.shared_ff); }
     }
@@ -80,6 +82,7 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
     z.q = a.take(Tz * hd * es);
     z.q_abs = (float*)a.take(Tz * hkv * 4);
     z.o_lat = a.take(Tz * hkv * es);
+    z.kv = a.take(Tz * hkvw * es);
     z.la_part_bytes = (size_t)512 * ((size_t)hkv + 2 * (size_t)hmax) * 4;      // tokens x splits <= 512
     z.la_part = (float*)a.take(z.la_part_bytes);
     z.mix_out = (float*)a.take(Tz * W * 4);
@@ -138,14 +141,25 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
             UMBS_TRY(umbs_latent_norm(dt, s.proj, T, l.q_rank, R, l.q_norm, l.kv_norm, m->norm_eps, s.cq, s.c, stream));
             UMBS_TRY(umbs_gemm(dt, s.cq, l.q_rank, 0, l.w_uq, l.q_rank, 0, s.q, hd, 0, 0, T, hd, l.q_rank, 1, nullptr, nullptr, 0,
                                0.f, stream));
-            // q_abs[t, h, :] = W_uk[h]^T q[t, h, :]: scores against the cached latents need no per-key up-projection
-            UMBS_TRY(umbs_gemm(dt, s.q, hd, l.dim, l.w_ukT, l.dim, (int64_t)R * l.dim, s.q_abs, (int64_t)l.heads * R, R, 1, T, R,
-                               l.dim, l.heads, nullptr, nullptr, 0, 0.f, stream));
-            UMBS_TRY(umbs_latent_attention(dt, s.q_abs, s.c, l.ring, l.ring_len, b, l.heads, R, l.window, l.scale, s.la_part,
-                                           s.la_part_bytes, s.o_lat, stream));
-            UMBS_TRY(umbs_ring_append(dt, s.c, l.ring, l.ring_len, b, R, stream));
-            UMBS_TRY(umbs_gemm(dt, s.o_lat, (int64_t)l.heads * R, R, l.w_uv, R, (int64_t)l.vdim * R, s.mixed, hv, l.vdim, 0, T,
-                               l.vdim, R, l.heads, nullptr, nullptr, 0, 0.f, stream));
+            if (b->max_seq_len > 1 && b->max_pos0 == 0 && l.w_ukv != nullptr && umbs_window_attention_fits(l.dim, l.vdim)) {
+                // a step of fresh sequences: every visible key is in the step, so keys and values are up-projected once per
+                // token and attention runs over dim + vdim numbers per key instead of twice the latent rank
+                UMBS_TRY(umbs_gemm(dt, s.c, R, 0, l.w_ukv, R, 0, s.kv, hd + hv, 0, 0, T, hd + hv, R, 1, nullptr, nullptr, 0, 0.f,
+                                   stream));
+                const char* kvb = (const char*)s.kv;
+                UMBS_TRY(umbs_window_attention(dt, s.q, hd, kvb, hd + hv, kvb + (size_t)hd * (dt == UMBS_F32 ? 4 : 2), hd + hv, b,
+                                               l.heads, l.dim, l.vdim, l.window, l.scale, s.mixed, hv, stream));
+                UMBS_TRY(umbs_ring_append(dt, s.c, l.ring, l.ring_len, b, R, stream));
+            } else {
+                // q_abs[t, h, :] = W_uk[h]^T q[t, h, :]: scores against the cached latents need no per-key up-projection
+                UMBS_TRY(umbs_gemm(dt, s.q, hd, l.dim, l.w_ukT, l.dim, (int64_t)R * l.dim, s.q_abs, (int64_t)l.heads * R, R, 1, T, R,
+                                   l.dim, l.heads, nullptr, nullptr, 0, 0.f, stream));
+                UMBS_TRY(umbs_latent_attention(dt, s.q_abs, s.c, l.ring, l.ring_len, b, l.heads, R, l.window, l.scale, s.la_part,
+                                               s.la_part_bytes, s.o_lat, stream));
+                UMBS_TRY(umbs_ring_append(dt, s.c, l.ring, l.ring_len, b, R, stream));
+                UMBS_TRY(umbs_gemm(dt, s.o_lat, (int64_t)l.heads * R, R, l.w_uv, R, (int64_t)l.vdim * R, s.mixed, hv, l.vdim, 0, T,
+                                   l.vdim, R, l.heads, nullptr, nullptr, 0, 0.f, stream));
+            }
         } else {
             return UMB_ERR_UNSUPPORTED;
         }

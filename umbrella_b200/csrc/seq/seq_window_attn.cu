@@ -1,0 +1,183 @@
+// Sliding-window softmax attention over per-head keys and values that all sit in the step itself: the form a whole
+// prompt takes (no token of the step sees anything older than the step).  Keys and values are then up-projected once
+// per token by a matrix product and a (row, key) pair costs dim + vdim multiply-adds, where the latent form -- which a
+// decode step needs, because only latents are cached -- costs twice the latent rank.
+//
+// One block = 64 consecutive query rows of one (sequence, head); 256 threads as 16 x 16, a thread owns 4 rows x 4 keys
+// of the score tile and 4 rows x VC value columns of the output.  Per tile of 64 keys:
+//   scores   Q K^T from transposed fp32 tiles in shared memory (two 16-byte loads per 16 multiply-adds),
+//   softmax  running maximum / sum per row in fp32, reduced over the 16 threads that share the row,
+//   values   P V with P handed over through shared memory.
+// Everything is fp32 arithmetic; T is the storage type of q, k, v and the output.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "seq_internal.h"
+
+namespace umbs {
+
+constexpr int kWaQ = 64, kWaK = 64, kWaS = 68;        // rows and keys per tile; row stride of the [d][row] tiles
+
+template <typename T, int VC>
+__global__ void __launch_bounds__(256) window_attention_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ k,
+                                                               int64_t ldk, const T* __restrict__ v, int64_t ldv, Batch b,
+                                                               int dim, int vdim, int window, float scale,
+                                                               T* __restrict__ out, int64_t ldo) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int VW = 16 * VC, VP = VW + 4;          // value columns a block covers; row stride of the value tile
+    float* Qs = sm;                                   // [dim][kWaS]  Qs[d][row]
+    float* Ks = Qs + (size_t)dim * kWaS;              // [dim][kWaS]  Ks[d][key]
+    float* Vs = Ks + (size_t)dim * kWaS;              // [kWaK][VP]
+    float* Ps = Vs + (size_t)kWaK * VP;               // [kWaK][kWaS] Ps[key][row]
+    const int s = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * kWaQ;
+    const int len = b.seq_len[s], start = b.seq_start[s];
+    if (q0 >= len) return;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    for (int i = tid; i < kWaQ * dim; i += 256) {
+        const int r = i / dim, d = i - r * dim;
+        Qs[d * kWaS + r] = (q0 + r < len) ? to_f32(q[(int64_t)(start + q0 + r) * ldq + (int64_t)h * dim + d]) : 0.f;
+    }
+    float m[4], l[4], o[4][VC];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        m[i] = -INFINITY;
+        l[i] = 0.f;
+#pragma unroll
+        for (int c = 0; c < VC; ++c) o[i][c] = 0.f;
+    }
+    const int row_hi = min(len, q0 + kWaQ) - 1;       // last row of the block = last key any of its rows sees
+    for (int j0 = max(0, q0 - window + 1); j0 <= row_hi; j0 += kWaK) {
+        __syncthreads();                              // the previous tile is consumed (first time round: Qs is written)
+        for (int i = tid; i < kWaK * dim; i += 256) {
+            const int kk = i / dim, d = i - kk * dim, j = j0 + kk;
+            Ks[d * kWaS + kk] = j <= row_hi ? to_f32(k[(int64_t)(start + j) * ldk + (int64_t)h * dim + d]) : 0.f;
+        }
+        for (int i = tid; i < kWaK * VW; i += 256) {
+            const int kk = i / VW, c = i - kk * VW, j = j0 + kk;
+            Vs[kk * VP + c] = (j <= row_hi && c < vdim) ? to_f32(v[(int64_t)(start + j) * ldv + (int64_t)h * vdim + c]) : 0.f;
+        }
+        __syncthreads();
+        float sc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) sc[i][jj] = 0.f;
+        for (int d = 0; d < dim; ++d) {
+            const float4 qv = *reinterpret_cast<const float4*>(Qs + d * kWaS + ty * 4);
+            const float4 kv = *reinterpret_cast<const float4*>(Ks + d * kWaS + tx * 4);
+            const float qa[4] = {qv.x, qv.y, qv.z, qv.w}, ka[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) sc[i][jj] = fmaf(qa[i], ka[jj], sc[i][jj]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int rp = q0 + ty * 4 + i;           // the row's index in its sequence; only differences to keys matter
+            float val[4], mx = -INFINITY;
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const int j = j0 + tx * 4 + jj;
+                const bool vis = rp < len && j <= rp && j > rp - window;
+                val[jj] = vis ? sc[i][jj] * scale : -INFINITY;
+                mx = fmaxf(mx, val[jj]);
+            }
+#pragma unroll
+            for (int w = 8; w > 0; w >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, w));   // the row's 16 threads
+            const float mn = fmaxf(m[i], mx);
+            float p[4] = {0.f, 0.f, 0.f, 0.f}, sum = 0.f, corr = 1.f;
+            if (mn > -INFINITY) {
+                corr = expf(m[i] - mn);
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    p[jj] = val[jj] > -INFINITY ? expf(val[jj] - mn) : 0.f;
+                    sum += p[jj];
+                }
+            }
+#pragma unroll
+            for (int w = 8; w > 0; w >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
+            l[i] = l[i] * corr + sum;
+            m[i] = mn;
+#pragma unroll
+            for (int c = 0; c < VC; ++c) o[i][c] *= corr;
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) Ps[(tx * 4 + jj) * kWaS + ty * 4 + i] = p[jj];
+        }
+        __syncthreads();
+        for (int kk = 0; kk < kWaK; ++kk) {
+            const float4 pv = *reinterpret_cast<const float4*>(Ps + kk * kWaS + ty * 4);
+            const float pa[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+            for (int cb = 0; cb < VC / 4; ++cb) {
+                const float4 vv = *reinterpret_cast<const float4*>(Vs + kk * VP + cb * 64 + tx * 4);
+                const float va[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) o[i][cb * 4 + c] = fmaf(pa[i], va[c], o[i][cb * 4 + c]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = q0 + ty * 4 + i;
+        if (r >= len) continue;
+        const float inv = 1.f / l[i];
+        T* orow = out + (int64_t)(start + r) * ldo + (int64_t)h * vdim;
+#pragma unroll
+        for (int cb = 0; cb < VC / 4; ++cb)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int col = cb * 64 + tx * 4 + c;
+                if (col < vdim) orow[col] = from_f32<T>(o[i][cb * 4 + c] * inv);
+            }
+    }
+}
+
+template <typename T, int VC>
+static int launch_window_attention(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
+                                   const Batch& b, int heads, int dim, int vdim, int window, float scale, void* out,
+                                   int64_t ldo, cudaStream_t st) {
+    const size_t smem = ((size_t)2 * dim * kWaS + (size_t)kWaK * (16 * VC + 4) + (size_t)kWaK * kWaS) * sizeof(float);
+    static size_t set = 0;
+    if (smem > 48 * 1024 && smem > set) {
+        cudaError_t e = cudaFuncSetAttribute(window_attention_kernel<T, VC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        set = smem;
+    }
+    const dim3 grid((b.max_seq_len + kWaQ - 1) / kWaQ, heads, b.n_seqs);
+    window_attention_kernel<T, VC><<<grid, 256, smem, st>>>((const T*)q, ldq, (const T*)k, ldk, (const T*)v, ldv, b, dim, vdim,
+                                                            window, scale, (T*)out, ldo);
+    return 0;
+}
+
+}  // namespace umbs
+
+using namespace umbs;
+
+extern "C" int umbs_window_attention_fits(int dim, int vdim) { return dim >= 1 && dim <= 128 && vdim >= 1 && vdim <= 128; }
+
+extern "C" int umbs_window_attention(int dtype, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                                     int64_t ldv, const umbs_batch_t* batch, int heads, int dim, int vdim, int window,
+                                     float scale, void* out, int64_t ldo, umbs_stream_t stream) {
+    if (batch->n_tokens <= 0) return 0;
+    if (window < 1 || heads < 1) return UMB_ERR_ARG;
+    if (!umbs_window_attention_fits(dim, vdim)) return UMB_ERR_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc;
+    if (dtype == UMBS_BF16) {
+        rc = vdim <= 64 ? launch_window_attention<__nv_bfloat16, 4>(q, ldq, k, ldk, v, ldv, *batch, heads, dim, vdim, window, scale, out, ldo, st)
+                        : launch_window_attention<__nv_bfloat16, 8>(q, ldq, k, ldk, v, ldv, *batch, heads, dim, vdim, window, scale, out, ldo, st);
+    } else if (dtype == UMBS_F32) {
+        rc = vdim <= 64 ? launch_window_attention<float, 4>(q, ldq, k, ldk, v, ldv, *batch, heads, dim, vdim, window, scale, out, ldo, st)
+                        : launch_window_attention<float, 8>(q, ldq, k, ldk, v, ldv, *batch, heads, dim, vdim, window, scale, out, ldo, st);
+    } else {
+        return UMB_ERR_ARG;
+    }
+    if (rc) return rc;
+    count_launches(1);
+    return (int)cudaGetLastError();
+}

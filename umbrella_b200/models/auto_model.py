@@ -49,7 +49,7 @@ def _radanex(path, **kw):
     return radanex.from_pretrained(path, **kw)
 
 
-# config.json ``architecture`` -> factory(path, device=, dtype=, max_length=, slots=, max_tokens=)
+# config.json ``architecture`` -> factory(path, device=, dtype=, max_length=, slots=, max_tokens=, ...)
 _ARCHITECTURES = {"Radanex": _radanex}
 
 
@@ -58,7 +58,7 @@ def _make(model_name, offload=False, batch_size=1, max_length=None, device="cuda
     if arch in _ARCHITECTURES:
         if offload:
             raise ValueError(f"{arch}: weight offloading is not implemented for sequence-state decoders")
-        kw = {k: unused[k] for k in ("slots", "max_tokens") if k in unused}
+        kw = {k: unused[k] for k in ("slots", "max_tokens", "graph_decode", "fresh_attention") if k in unused}
         return _ARCHITECTURES[arch](str(model_name), device=device, dtype=torch.bfloat16 if dtype == torch.float16 else dtype,
                                     max_length=max_length, **kw)
     max_length = 256 if max_length is None else max_length          # the reference's default (models/base.py)

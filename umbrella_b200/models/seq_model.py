@@ -82,7 +82,7 @@ class SeqStateModel:
 
     def __init__(self, spec: SeqModelSpec, device="cuda:0", dtype=torch.bfloat16, slots: int = 8,
                  max_length: int | None = None, max_tokens: int = 0, model_name: str | None = None,
-                 graph_decode: bool = True):
+                 graph_decode: bool = True, fresh_attention: bool = True):
         if dtype not in (torch.bfloat16, torch.float32):
             raise TypeError("sequence-state decoders run in bfloat16 or float32")
         self.spec = self.config = spec
@@ -103,6 +103,9 @@ class SeqStateModel:
         # size has run eagerly twice: slots, positions and parities live in the device-side batch description, so the
         # same graph serves every later step of that size
         self.graph_decode = graph_decode
+        # latent attention of a step whose sequences all start at position 0 runs over per-head keys and values
+        # up-projected once per token (False: always over the latents, as decode steps and later portions do)
+        self.fresh_attention = fresh_attention
         self._graphs: dict = {}
         self._graph_seen: dict = {}
 
@@ -162,6 +165,8 @@ class SeqStateModel:
             # key up-projection transposed per head: [heads, dim, kv_rank] -> [heads, kv_rank, dim]
             d["ukT"] = self._act(w["uk"].reshape(l.heads, l.dim, l.kv_rank).transpose(1, 2))
             d["uv"] = self._act(w["uv"])
+            # key rows then value rows in one matrix: a step of fresh sequences up-projects its latents with one product
+            d["ukv"] = self._act(torch.cat([w["uk"], w["uv"]], dim=0))
             assert d["uq"].shape == (l.heads * l.dim, l.q_rank) and d["uv"].shape == (l.heads * l.vdim, l.kv_rank)
         else:
             raise ValueError(f"unknown mixer '{l.mixer}'")
@@ -206,6 +211,7 @@ class SeqStateModel:
                 cl.scale = l.scale
                 cl.q_norm, cl.kv_norm, cl.w_uq, cl.w_ukT, cl.w_uv = p(w["q_norm"]), p(w["kv_norm"]), p(w["uq"]), \
                     p(w["ukT"]), p(w["uv"])
+                cl.w_ukv = p(w["ukv"]) if self.fresh_attention else None
                 cl.ring = p(cache.ring[i])
             cl.w_in, cl.w_o, cl.norm_w = p(w["w_in"]), p(w["o"]), p(w["norm"])
             cl.shift_w, cl.shift_state = p(w.get("shift")), p(cache.shift[i])
@@ -262,6 +268,7 @@ class SeqStateModel:
         def describe(base):
             bt, o = S.Batch(), 0
             bt.n_tokens, bt.n_seqs, bt.n_want, bt.max_seq_len = T, B, Wn, max(length)
+            bt.max_pos0 = max(pos0)
             for name, n in (("tok_ids", T), ("tok_seq", T), ("tok_pos", T), ("seq_slot", B), ("seq_start", B),
                             ("seq_len", B), ("seq_pos0", B), ("seq_parity", B), ("want_rows", Wn)):
                 setattr(bt, name, base + 4 * o)

@@ -52,6 +52,7 @@ class RaggedBatch:
         c = S.Batch()
         c.n_tokens, c.n_seqs, c.n_want = T, len(seqs), len(want) if want is not None else 0
         c.max_seq_len = max(s[1] for s in seqs) if seqs else 0
+        c.max_pos0 = max(s[2] for s in seqs) if seqs else 0
         for k, v in self.t.items():
             setattr(c, k, v.data_ptr())
         self.c, self.n_tokens = c, T
@@ -116,6 +117,19 @@ def latent_norm(x, q_rank, kv_rank, q_norm, kv_norm, eps, dtype=torch.float32):
     S.check(S.load().umbs_latent_norm(_mode(c), _p(x), n, q_rank, kv_rank, _p(q_norm), _p(kv_norm), float(eps), _p(cq), _p(c),
                                       _stream()), "latent_norm")
     return cq, c
+
+
+def window_attention(q, k, v, batch: RaggedBatch, heads: int, window: int, scale: float):
+    """q, k [T, heads dim], v [T, heads vdim] (views with a row stride are fine) -> [T, heads vdim]: sliding-window
+    softmax attention among the step's own tokens (fresh sequences)."""
+    T = q.shape[0]
+    dim, vdim = q.shape[1] // heads, v.shape[1] // heads
+    assert q.stride(1) == k.stride(1) == v.stride(1) == 1
+    out = torch.empty((T, heads * vdim), dtype=q.dtype, device=q.device)
+    S.check(S.load().umbs_window_attention(_mode(q), _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0),
+                                           C.byref(batch.c), heads, dim, vdim, window, float(scale), _p(out), heads * vdim,
+                                           _stream()), "window_attention")
+    return out
 
 
 def moe_route(h, w_router, top: int):

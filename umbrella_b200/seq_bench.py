@@ -189,6 +189,14 @@ def kernel_table(rm, lm, device, timer, T=4096):
         keys = sum(min(p + 1, lat.window) for p in range(per)) * nseq if n == T else n * min(513, lat.window)
         add(f"latent attention, window {lat.window}, fp32 scores ({tag})", ms,
             nbytes=n * lat.heads * R * (4 + 2) + (n * R * 2 if n == T else keys * R * 2), flops32=4 * keys * lat.heads * R)
+        if n == T:
+            # the form a step of fresh sequences takes: per-head keys | values up-projected once, then attention over them
+            hd, hvv = lat.heads * lat.dim, lat.heads * lat.vdim
+            qh = torch.randn(n, hd, **bf)
+            kvh = torch.randn(n, hd + hvv, **bf)
+            ms = timer(lambda: Q.window_attention(qh, kvh[:, :hd], kvh[:, hd:], batch, lat.heads, lat.window, lat.scale))
+            add(f"window attention over per-head keys, window {lat.window}, fp32 scores ({tag})", ms,
+                nbytes=n * (2 * hd + 2 * hvv) * 2, flops32=2 * keys * lat.heads * (lat.dim + lat.vdim))
         # residual + depth mix
         stack = torch.randn(len(sp.layers) + 1, n, W, device=device)
         mix = torch.randn(n, W, device=device)
