@@ -142,10 +142,12 @@ int umbs_group_norm_rows(int dtype, const float* x, const int32_t* rows, int n_r
 /* Decayed linear attention over qkvg = [q | k | v | g] (fp32 [n_tokens, ld]): rotary (rotate-half pairs, the first
  * rot_dims dimensions, angle = position * inv_freq[i]) on q and k, k *= dim^-1/2, S <- decay_h S + k v^T, o = S^T q,
  * o / rms(o) per head, * silu(g) -> out (`dtype` [n_tokens, heads vdim]).  state: fp32 [slots, heads, dim, vdim];
- * o_scratch: fp32 [n_tokens, heads vdim]; rot_scratch: fp32 [n_tokens, rot_dims] (the step's cos | sin table). */
+ * o_scratch: fp32 [n_tokens, heads vdim]; rot_scratch: fp32 [n_tokens, rot_dims] (the step's cos | sin table).
+ * seg_scratch (optional, fp32, seg_bytes): room for segment states, heads dim vdim floats each.  With it a step of few
+ * long sequences is cut into segments that run side by side in two passes; as many segments as fit are used. */
 int umbs_retention(int dtype, const float* qkvg, int64_t ld, const umbs_batch_t* batch, int heads, int dim, int vdim,
                    int rot_dims, const float* inv_freq, const float* decay, float eps, float* state, float* o_scratch,
-                   float* rot_scratch, void* out, umbs_stream_t stream);
+                   float* rot_scratch, float* seg_scratch, size_t seg_bytes, void* out, umbs_stream_t stream);
 
 /* Plain RMS norms of the two latents: x (fp32 [n, q_rank + kv_rank]) -> cq (`dtype` [n, q_rank]), c (`dtype` [n, kv_rank]). */
 int umbs_latent_norm(int dtype, const float* x, int n, int q_rank, int kv_rank, const float* q_norm, const float* kv_norm,

@@ -152,6 +152,39 @@ def test_retention_whole_portions_and_batch(ops, Hh, D, V, rot):
     assert H.row_err(torch.cat(outs), ref) < 2e-5 and H.row_err(torch.cat(outs2), ref2) < 2e-5
 
 
+def test_retention_long_sequences_cut_into_segments(ops):
+    """Few long sequences run as segments side by side (two passes with chained states): the same numbers as the single
+    walk and as the oracle -- for a fresh sequence, for one that goes on from a carried state, next to a short one that is
+    not cut, and with a last segment of a few tokens."""
+    from umbrella_b200.models.seq_model import rotary_inv_freq
+    Hh, D, V, rot, base, eps = 2, 16, 40, 8, 50.0, 1e-4
+    decay = [0.93, 0.9995]
+    inv, dec = rotary_inv_freq(rot, base).to(DEV), torch.tensor(decay, device=DEV)
+    n = 700
+    qkvg, q, k, v, gt = _ret_inputs(n, Hh, D, V, 23)
+    ref = _ret_ref(q, k, v, gt, D, rot, base, decay, eps)
+    other, q2, k2, v2, g2 = _ret_inputs(40, Hh, D, V, 24)
+    ref2 = _ret_ref(q2, k2, v2, g2, D, rot, base, decay, eps)
+    x, y = qkvg.to(DEV), other.to(DEV)
+    for segments in (True, False):
+        state = torch.full((3, Hh, D, V), 7.0, device=DEV)
+        # step 1: 130 tokens of the long one; step 2: its other 570 (a carried state, cut) next to a fresh short one
+        o1 = ops.retention(x[:130].contiguous(), ops.RaggedBatch([(2, 130, 0, 0)], DEV), Hh, D, V, rot, inv, dec, eps, state,
+                           segments=segments)
+        o2 = ops.retention(torch.cat([x[130:], y]), ops.RaggedBatch([(2, 570, 130, 0), (0, 40, 0, 0)], DEV), Hh, D, V, rot, inv,
+                           dec, eps, state, segments=segments)
+        assert H.row_err(torch.cat([o1, o2[:570]]), ref) < 2e-5, segments
+        assert H.row_err(o2[570:], ref2) < 2e-5, segments
+        if segments:
+            cut_state = state.clone()
+        else:
+            assert H.rel_err(cut_state[2], state[2]) < 1e-5 and H.rel_err(cut_state[0], state[0]) < 1e-6
+    # a length that leaves a last segment of one token
+    state = torch.zeros((1, Hh, D, V), device=DEV)
+    o = ops.retention(x[:385].contiguous(), ops.RaggedBatch([(0, 385, 0, 0)], DEV), Hh, D, V, rot, inv, dec, eps, state)
+    assert H.row_err(o, ref[:385]) < 2e-5
+
+
 def test_retention_carries_one_far_key(ops):
     """Only token 0 has a key and a value; the query sits 400 tokens later, reached through four separate steps."""
     Hh, D, V, n, decay = 1, 8, 32, 401, 0.99609375

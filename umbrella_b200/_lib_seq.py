@@ -61,7 +61,7 @@ SIGNATURES = {
                                       c_void_p, c_void_p, c_void_p]),
     "umbs_group_norm_rows": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p]),
     "umbs_retention": (c_int, [c_int, c_void_p, c_int64, _BP, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
-                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "umbs_latent_norm": (c_int, [c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                  c_void_p]),
     "umbs_latent_attention": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, _BP, c_int, c_int, c_int, c_float,

@@ -29,6 +29,8 @@ struct Scratch {
     float* proj;       // fp32 [T, max in-projection rows]
     float* o32;        // fp32 [T, max(heads vdim)]  retention outputs before the gate
     float* rot;        // fp32 [T, max rot_dims]     the step's cos | sin table
+    float* seg;        // fp32 segment states of a retention step cut into segments
+    size_t seg_bytes;
     void* mixed;       // act [T, max(heads vdim)]   mixer output before W_o
     void* cq;          // act [T, max q_rank]
     void* c;           // act [T, max kv_rank]
@@ -53,12 +55,18 @@ struct Scratch {
 
 static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratch* s) {
     const size_t es = m->dtype == UMBS_F32 ? 4 : 2;
+    size_t segb = 0;
     int hmax = 1, rotd = 1, in_rows = 1, hv = 1, qr = 1, kvr = 1, hd = 1, hkv = 1, hkvw = 1, top = 1, experts = 1, ff = 1, sff = 1;
     for (int i = 0; i < m->n_layers; ++i) {
         const umbs_layer_t& l = m->layers[i];
         auto up = [](int& a, int b) { if (b > a) a = b; };
         up(hv, l.heads * l.vdim);
-        if (l.mixer == UMBS_MIX_RETENTION) { up(in_rows, 2 * l.heads * l.dim + 2 * l.heads * l.vdim); up(rotd, l.rot_dims); }
+        if (l.mixer == UMBS_MIX_RETENTION) {
+            up(in_rows, 2 * l.heads * l.dim + 2 * l.heads * l.vdim); up(rotd, l.rot_dims);
+            // segment states of a step of few long sequences: about 592 blocks' worth (umbs_retention uses what fits)
+            const size_t plane = (size_t)l.heads * l.dim * l.vdim * 4, ent = 592 / ((size_t)l.heads * ((l.vdim + 31) / 32)) + 8;
+            if (T >= 128 && ent * plane > segb) segb = ent * plane;
+        }
         else {
             up(in_rows, l.q_rank + l.kv_rank);
             up(hmax, l.heads); up(qr, l.q_rank); up(kvr, l.kv_rank); up(hd, l.heads * l.dim); up(hkv, l.heads * l.kv_rank);
@@ -76,6 +84,8 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
     z.proj = (float*)a.take(Tz * in_rows * 4);
     z.o32 = (float*)a.take(Tz * hv * 4);
     z.rot = (float*)a.take(Tz * rotd * 4);
+    z.seg_bytes = segb;
+    z.seg = (float*)a.take(segb);
     z.mixed = a.take(Tz * hv * es);
     z.cq = a.take(Tz * qr * es);
     z.c = a.take(Tz * kvr * es);
@@ -134,7 +144,7 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
             const int rows = 2 * l.heads * l.dim + 2 * hv;
             UMBS_TRY(umbs_gemm(dt, hs, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
             UMBS_TRY(umbs_retention(dt, s.proj, rows, b, l.heads, l.dim, l.vdim, l.rot_dims, l.inv_freq, l.decay,
-                                    m->norm_eps, l.ret_state, s.o32, s.rot, s.mixed, stream));
+                                    m->norm_eps, l.ret_state, s.o32, s.rot, s.seg_bytes ? s.seg : nullptr, s.seg_bytes, s.mixed, stream));
         } else if (l.mixer == UMBS_MIX_LATENT_ATTENTION) {
             const int rows = l.q_rank + l.kv_rank, hd = l.heads * l.dim, R = l.kv_rank;
             UMBS_TRY(umbs_gemm(dt, hs, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));

@@ -149,23 +149,45 @@ __global__ void rotary_table_kernel(const int32_t* __restrict__ tok_pos, const f
 template <int DPT, int kRetTB>
 __global__ void retention_kernel(const float* __restrict__ qkvg, int64_t ld, Batch b, int heads, int dim, int vdim,
                                  int rot_dims, const float* __restrict__ rot_tab, const float* __restrict__ inv_freq,
-                                 const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ o_out) {
+                                 const float* __restrict__ decay, float* __restrict__ state, float* __restrict__ o_out,
+                                 int seg_len, int n_seg, int pass, float* __restrict__ seg_state) {
     extern __shared__ __align__(16) float sm[];
     const int DS = blockDim.y, dimP = DS * DPT, nthr = 32 * DS;
     float* qs = sm;                          // [TB][dimP]
     float* ks = qs + kRetTB * dimP;          // [TB][dimP]
     float* part = ks + kRetTB * dimP;        // [DS][TB][32]
-    const int s = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, w = threadIdx.y, tid = w * 32 + lane;
+    // A sequence may be cut into n_seg segments of seg_len tokens that run as blocks of their own (blockIdx.x =
+    // sequence * n_seg + segment).  pass 0: no segments, the block walks the whole sequence.  pass 1: every segment but a
+    // sequence's last starts from zero and leaves its end state in seg_state (no outputs).  Between the passes
+    // retention_chain_kernel turns these into the segments' true start states.  pass 2: every segment starts from its
+    // entry of seg_state; outputs are written, and the last segment stores the slot's state.
+    const int s = blockIdx.x / n_seg, seg = blockIdx.x - s * n_seg;
+    const int h = blockIdx.y, lane = threadIdx.x, w = threadIdx.y, tid = w * 32 + lane;
     const int j = blockIdx.z * 32 + lane, d0 = w * DPT;
-    const int start = b.seq_start[s], len = b.seq_len[s], pos0 = b.seq_pos0[s], slot = b.seq_slot[s];
+    const int seq_len = b.seq_len[s], t_first = seg * seg_len;
+    if (t_first >= seq_len) return;
+    const int len = min(seg_len, seq_len - t_first), start = b.seq_start[s] + t_first;
+    const bool last_seg = t_first + len == seq_len;
+    if (pass == 1 && last_seg) return;
+    const int pos0 = b.seq_pos0[s], slot = b.seq_slot[s];
     const bool col = j < vdim;
+    const int64_t plane = (int64_t)heads * dim * vdim;
     const float dec = decay[h];
     const float kscale = 1.f / sqrtf((float)dim);
     const int half = rot_dims / 2;
     float* st = state + (((int64_t)slot * heads + h) * dim) * vdim;
+    const float* st_in = st;
+    bool have = pos0 > 0;
+    if (pass == 1) have = false;
+    else if (pass == 2 && !(seg == 0 && last_seg)) {
+        // segment 0 of a cut sequence reads the chain kernel's copy of the slot's state (entry n_seg - 1), not the slot,
+        // which the sequence's last segment overwrites during this very launch
+        st_in = seg_state + ((int64_t)s * n_seg + (seg > 0 ? seg - 1 : n_seg - 1)) * plane + (int64_t)h * dim * vdim;
+        have = true;
+    }
     float S[DPT];
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) S[i] = (col && pos0 > 0 && d0 + i < dim) ? st[(int64_t)(d0 + i) * vdim + j] : 0.f;
+    for (int i = 0; i < DPT; ++i) S[i] = (col && have && d0 + i < dim) ? st_in[(int64_t)(d0 + i) * vdim + j] : 0.f;
     const int qoff = h * dim, koff = heads * dim + h * dim, voff = 2 * heads * dim + h * vdim;
     // Each thread stages EPT (token, dim) elements of q and k and up to TB values of v per round; the loads of round
     // r + 1 are issued before round r is consumed, so their latency hides behind the serial walk through the tokens.
@@ -242,7 +264,7 @@ __global__ void retention_kernel(const float* __restrict__ qkvg, int64_t ld, Bat
             part[(w * kRetTB + tt) * 32 + lane] = acc;
         }
         __syncthreads();
-        for (int i = tid; i < nb * 32; i += nthr) {
+        for (int i = tid; i < nb * 32 && pass != 1; i += nthr) {
             const int tt = i >> 5, l = i & 31, jj = blockIdx.z * 32 + l;
             if (jj >= vdim) continue;
             float o = 0.f;
@@ -250,10 +272,35 @@ __global__ void retention_kernel(const float* __restrict__ qkvg, int64_t ld, Bat
             o_out[(int64_t)(start + t0 + tt) * ((int64_t)heads * vdim) + h * vdim + jj] = o;
         }
     }
+    float* st_out = st;
+    if (pass == 1) st_out = seg_state + ((int64_t)s * n_seg + seg) * plane + (int64_t)h * dim * vdim;
+    else if (pass == 2 && !last_seg) return;
     if (col) {
 #pragma unroll
         for (int i = 0; i < DPT; ++i)
-            if (d0 + i < dim) st[(int64_t)(d0 + i) * vdim + j] = S[i];
+            if (d0 + i < dim) st_out[(int64_t)(d0 + i) * vdim + j] = S[i];
+    }
+}
+
+// Between the two passes of a segmented step: seg_state[s][g] holds the end state L_g of segment g run from zero; the
+// state segment g + 1 starts from is S_(g+1) = decay^seg_len S_g + L_g with S_0 the slot's state (zero for a fresh
+// sequence).  One thread per state element walks the segments in order and overwrites L_g with S_(g+1).
+__global__ void retention_chain_kernel(Batch b, int heads, int dim, int vdim, const float* __restrict__ decay,
+                                       const float* __restrict__ state, int seg_len, int n_seg, float* __restrict__ seg_state) {
+    const int64_t plane = (int64_t)heads * dim * vdim;
+    const int s = blockIdx.y;
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= plane) return;
+    const int full = (b.seq_len[s] - 1) / seg_len;          // segments that are followed by another one
+    if (full <= 0) return;
+    const int h = (int)(e / ((int64_t)dim * vdim));
+    const float dn = powf(decay[h], (float)seg_len);
+    float S = b.seq_pos0[s] > 0 ? state[(int64_t)b.seq_slot[s] * plane + e] : 0.f;
+    float* p = seg_state + (int64_t)s * n_seg * plane + e;
+    p[(int64_t)(n_seg - 1) * plane] = S;                    // entry n_seg - 1 never holds an end state: segment 0's start state
+    for (int g = 0; g < full; ++g) {
+        S = fmaf(dn, S, p[(int64_t)g * plane]);
+        p[(int64_t)g * plane] = S;
     }
 }
 
@@ -695,9 +742,9 @@ extern "C" int umbs_group_norm_rows(int dtype, const float* x, const int32_t* ro
 template <int DPT, int kRetTB>
 static int launch_retention(const float* qkvg, int64_t ld, const Batch& b, int heads, int dim, int vdim, int rot_dims,
                             const float* rot_tab, const float* inv_freq, const float* decay, float* state, float* o,
-                            cudaStream_t st) {
+                            int seg_len, int n_seg, int pass, float* seg_state, cudaStream_t st) {
     const int ds = (dim + DPT - 1) / DPT;
-    const dim3 grid(b.n_seqs, heads, (vdim + 31) / 32), block(32, ds);
+    const dim3 grid(b.n_seqs * n_seg, heads, (vdim + 31) / 32), block(32, ds);
     const size_t smem = ((size_t)2 * kRetTB * ds * DPT + (size_t)ds * kRetTB * 32 + kRetTB * 32) * sizeof(float);
     static size_t set = 0;
     if (smem > 48 * 1024 && smem > set) {
@@ -706,13 +753,14 @@ static int launch_retention(const float* qkvg, int64_t ld, const Batch& b, int h
         set = smem;
     }
     retention_kernel<DPT, kRetTB><<<grid, block, smem, st>>>(qkvg, ld, b, heads, dim, vdim, rot_dims, rot_tab, inv_freq, decay,
-                                                             state, o);
+                                                             state, o, seg_len, n_seg, pass, seg_state);
     return 0;
 }
 
 extern "C" int umbs_retention(int dtype, const float* qkvg, int64_t ld, const umbs_batch_t* batch, int heads, int dim,
                               int vdim, int rot_dims, const float* inv_freq, const float* decay, float eps, float* state,
-                              float* o_scratch, float* rot_scratch, void* out, umbs_stream_t stream) {
+                              float* o_scratch, float* rot_scratch, float* seg_scratch, size_t seg_bytes, void* out,
+                              umbs_stream_t stream) {
     if (batch->n_tokens <= 0) return 0;
     if (rot_dims < 0 || rot_dims > dim || (rot_dims & 1)) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
@@ -725,11 +773,38 @@ extern "C" int umbs_retention(int dtype, const float* qkvg, int64_t ld, const um
         rot_tab = rot_scratch;
         ++launches;
     }
+    // Few blocks and long sequences (one long prompt): cut the sequences into segments that run side by side, in two
+    // passes (local end states from zero, chained into start states, then the outputs).  Twice the arithmetic of the
+    // recurrence for n_seg times the blocks; the result differs from the single walk by fp32 rounding only.
+    int n_seg = 1, seg_len = batch->max_seq_len;
+    const int base_blocks = batch->n_seqs * heads * ((vdim + 31) / 32);
+    if (seg_scratch != nullptr && base_blocks <= 148 && batch->max_seq_len >= 128) {     // less than a block per SM
+        int want = std::min((592 + base_blocks - 1) / base_blocks, batch->max_seq_len / 64);
+        const size_t fit = seg_bytes / ((size_t)batch->n_seqs * heads * dim * vdim * sizeof(float));
+        want = (int)std::min<size_t>(want, fit);
+        if (want >= 2) {
+            seg_len = ((batch->max_seq_len + want - 1) / want + 15) & ~15;
+            n_seg = (batch->max_seq_len + seg_len - 1) / seg_len;
+        }
+    }
+    auto run = [&](int pass) -> int {
+        if (dim <= 32) return launch_retention<8, 16>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_tab, inv_freq, decay, state, o_scratch, seg_len, n_seg, pass, seg_scratch, st);
+        if (dim <= 128) return launch_retention<16, 16>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_tab, inv_freq, decay, state, o_scratch, seg_len, n_seg, pass, seg_scratch, st);
+        if (dim <= 512) return launch_retention<32, 8>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_tab, inv_freq, decay, state, o_scratch, seg_len, n_seg, pass, seg_scratch, st);
+        return UMB_ERR_UNSUPPORTED;
+    };
     int rc;
-    if (dim <= 32) rc = launch_retention<8, 16>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_tab, inv_freq, decay, state, o_scratch, st);
-    else if (dim <= 128) rc = launch_retention<16, 16>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_tab, inv_freq, decay, state, o_scratch, st);
-    else if (dim <= 512) rc = launch_retention<32, 8>(qkvg, ld, *batch, heads, dim, vdim, rot_dims, rot_tab, inv_freq, decay, state, o_scratch, st);
-    else return UMB_ERR_UNSUPPORTED;
+    if (n_seg > 1) {
+        rc = run(1);
+        if (rc) return rc;
+        const int64_t plane = (int64_t)heads * dim * vdim;
+        retention_chain_kernel<<<dim3((unsigned)((plane + 255) / 256), batch->n_seqs), 256, 0, st>>>(*batch, heads, dim, vdim, decay, state,
+                                                                                                 seg_len, n_seg, seg_scratch);
+        launches += 2;
+        rc = run(2);
+    } else {
+        rc = run(0);
+    }
     if (rc) return rc;
     const int warps = batch->n_tokens * heads;
     UMBS_DISPATCH_T(dtype, retention_gate_kernel<T><<<(warps + 3) / 4, 128, 0, st>>>(o_scratch, qkvg, ld, batch->n_tokens,

@@ -86,13 +86,17 @@ def group_norm_shift(x, w, shift_w, shift_state, batch: RaggedBatch, groups: int
     return h, hs
 
 
-def retention(qkvg, batch: RaggedBatch, heads, dim, vdim, rot_dims, inv_freq, decay, eps, state, dtype=torch.float32):
+def retention(qkvg, batch: RaggedBatch, heads, dim, vdim, rot_dims, inv_freq, decay, eps, state, dtype=torch.float32,
+              segments: bool = True):
+    """``segments``: give the kernel room to cut few long sequences into segments that run side by side."""
     T = qkvg.shape[0]
+    seg = torch.empty(32 * heads * dim * vdim, dtype=torch.float32, device=qkvg.device) if segments and T >= 128 else None
     o32 = torch.empty((T, heads * vdim), dtype=torch.float32, device=qkvg.device)
     out = torch.empty((T, heads * vdim), dtype=dtype, device=qkvg.device)
     rot = torch.empty((T, max(rot_dims, 1)), dtype=torch.float32, device=qkvg.device)
     S.check(S.load().umbs_retention(_mode(out), _p(qkvg), qkvg.stride(0), C.byref(batch.c), heads, dim, vdim, rot_dims,
-                                    _p(inv_freq), _p(decay), float(eps), _p(state), _p(o32), _p(rot), _p(out), _stream()),
+                                    _p(inv_freq), _p(decay), float(eps), _p(state), _p(o32), _p(rot), _p(seg),
+                                    seg.numel() * 4 if seg is not None else 0, _p(out), _stream()),
             "retention")
     return out
 
