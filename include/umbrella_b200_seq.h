@@ -33,6 +33,24 @@ typedef void* umbs_stream_t; /* cudaStream_t */
 
 #define UMBS_MIX_RETENTION 0
 #define UMBS_MIX_LATENT_ATTENTION 1
+#define UMBS_MIX_CACHED_ATTENTION 2  /* grouped-query attention over a per-slot key/value cache; options: window, pooled
+                                      * blocks of older keys, sink or sigmoid weights, short convolution on q and k,
+                                      * values = unrotated keys, output gate per head or per element */
+#define UMBS_MIX_MLSTM 3             /* matrix memory with exponential gates and a running maximum */
+
+/* How a layer is put together.  PARALLEL: one group norm feeds the mixer (token-shifted) and the feed-forward side by
+ * side, the sum goes through the depth average.  PRENORM: x += mixer(norm1(x)), then x += ff(norm2(x)). */
+#define UMBS_FORM_PARALLEL 0
+#define UMBS_FORM_PRENORM 1
+
+/* Gated activation of a gate|up pair of products (the `dual` argument of umbs_gemm; 0 = plain product). */
+#define UMBS_ACT_CLAMPED_GLU 1       /* g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit) */
+#define UMBS_ACT_GELU_TANH 2         /* gelu_tanh(g) u */
+
+/* How attention turns scores into weights. */
+#define UMBS_ATTN_SOFTMAX 0          /* p = exp(s) / sum exp(s) */
+#define UMBS_ATTN_SOFTMAX_SINK 1     /* p = exp(s) / (1 + sum exp(s)): a sink of score 0 without a value */
+#define UMBS_ATTN_SIGMOID 2          /* p = sigmoid(s + bias[head]), not normalised over keys */
 
 /* One step's ragged batch.  Token t of the step belongs to sequence tok_seq[t] (an index into the seq_* arrays)
  * and sits at absolute position tok_pos[t]; a sequence's tokens are contiguous: [seq_start, seq_start + seq_len).
@@ -52,8 +70,8 @@ typedef struct {
     int max_pos0;             /* host copy of the largest seq_pos0: 0 = every sequence of the step is fresh */
 } umbs_batch_t;
 
-/* Gated feed-forward block: y = W_down( act(W_gate h, W_up h) ), act(g, u) = g' sigmoid(1.702 g') (u' + 1) with
- * g' = min(g, limit), u' = clamp(u, -limit, limit).  w_gu holds the gate rows followed by the up rows, per expert. */
+/* Gated feed-forward block: y = W_down( act(W_gate h, W_up h) ), act = UMBS_ACT_* (0 reads as UMBS_ACT_CLAMPED_GLU).
+ * w_gu holds the gate rows followed by the up rows, per expert.  A dense feed-forward is a shared expert alone. */
 typedef struct {
     int experts, top, ff;      /* experts == 0: no routed part */
     float limit;
@@ -64,6 +82,7 @@ typedef struct {
     float shared_limit;
     const void* ws_gu;         /* [2 shared_ff, width] */
     const void* ws_down;       /* [width, shared_ff] */
+    int act;                   /* UMBS_ACT_* of both parts */
 } umbs_mlp_t;
 
 typedef struct {
@@ -94,6 +113,34 @@ typedef struct {
     const float* depth_w;      /* fp32 [layer index + 2] or NULL (no depth average) */
     int has_mlp;
     umbs_mlp_t mlp;
+    /* pre-norm form and the mixers that come with it */
+    int form;                  /* UMBS_FORM_* */
+    float norm_offset;         /* added to every norm weight of the layer (1: weights stored around zero) */
+    const float* norm2_w;      /* fp32 [width]: the norm in front of the feed-forward (PRENORM with a feed-forward) */
+    /* cached attention (uses heads, dim, vdim, rot_dims, inv_freq, window (0: every earlier token), scale from above);
+     * w_in rows: q (heads dim) | k (kv_heads dim) | v (kv_heads vdim; absent with values_are_keys) | gate (heads, heads
+     * vdim or none, by gate_kind) */
+    int kv_heads;              /* query head h reads key/value head h / (heads / kv_heads) */
+    int attn_mode;             /* UMBS_ATTN_* */
+    int gate_kind;             /* 0: no output gate, 1: sigmoid of one number per head, 2: of one per output element */
+    int values_are_keys;       /* the values are the keys as they are before the rotation (vdim = dim, no value rows) */
+    int pool;                  /* tokens per pooled block of keys that have left the window (0: none) */
+    int taps;                  /* taps of the short causal convolution on q and k (1: none) */
+    float rot_mag;             /* factor on cos and sin (inv_freq holds the scaled frequencies) */
+    float gate_cap;            /* mlstm: soft cap of the gate pre-activations */
+    const float* bias_in;      /* fp32 [rows of w_in] or NULL */
+    const float* conv_w;       /* fp32 [heads dim + kv_heads dim, taps] */
+    const float* head_bias;    /* fp32 [heads] or NULL: added to the scores (UMBS_ATTN_SIGMOID) */
+    const float* out_norm_w;   /* fp32 [heads vdim]: mlstm's weight after the per-head unit norm */
+    void* kv_cache;            /* act dtype [slots, kv_len, kv_heads (dim + vdim)]: keys then values of a token; position p at
+                                * row p mod kv_len (with a window: a ring of at least max(window, pool) rows; without:
+                                * every token of the sequence) */
+    int kv_len;
+    void* pool_cache;          /* act dtype [slots, pool_len, kv_heads (dim + vdim)]: mean key | mean value per block */
+    int pool_len;
+    float* conv_state;         /* fp32 [2, slots, taps - 1, heads dim + kv_heads dim]: the last projected q | k rows
+                                * (double-buffered by the sequence's parity, as the shift state) */
+    float* mlstm_state;        /* fp32 [slots, heads, dim (vdim + 1) + 1]: S with n as column vdim, then m */
 } umbs_layer_t;
 
 typedef struct {
@@ -104,6 +151,8 @@ typedef struct {
     const float* final_norm;   /* fp32 [width] */
     const void* head;          /* [vocab, width] */
     const umbs_layer_t* layers;/* host array */
+    float norm_offset;         /* added to the final norm's weight */
+    float logit_softcap;       /* > 0: logits <- cap tanh(logits / cap) */
 } umbs_model_t;
 
 const char* umbs_version(void);
@@ -189,6 +238,60 @@ int umbs_moe_route(int dtype, const void* h, int n, int width, const float* w_ro
 int umbs_depth_mix(const float* x, const float* mix, const float* pair_out, const float* sel_w, const int32_t* pair_pos,
                    int top, const float* shared, float* stack, int layer, const float* depth_w, float* x_out,
                    float* copy_out, int n, int width, umbs_stream_t stream);
+
+/* ---- pre-norm layers: residual + norm, the attention kinds over a per-slot key/value cache, mLSTM ---- */
+
+/* Residual add and RMS norm in one pass.  rows == NULL: for every row t < n: x[t] += delta[t] (delta may be NULL),
+ * copy[t] = x[t] (copy may be NULL), y[t] = x[t] / sqrt(mean(x[t]^2) + eps) * (w_offset + w) as `dtype` (y may be NULL).
+ * rows != NULL: y[r] is the norm of x[rows[r]] + delta[rows[r]], r < n; x is not written. */
+int umbs_add_rms_norm(int dtype, float* x, const float* delta, const int32_t* rows, int n, const float* w, float w_offset,
+                      int width, float eps, void* y, float* copy, umbs_stream_t stream);
+
+/* z <- cap tanh(z / cap), fp32, n values. */
+int umbs_softcap(float* z, int64_t n, float cap, umbs_stream_t stream);
+
+/* Queries, keys and values of an attention layer from its in-projection.  proj: fp32 [n_tokens, ld] = [q (heads dim) |
+ * k (kv_heads dim) | v (kv_heads vdim, absent when values are the keys) | gate ...].  Adds bias (or NULL), runs the
+ * causal convolution of `taps` taps over q and k (conv_w fp32 [heads dim + kv_heads dim, taps]; the rows before a
+ * sequence's step come from conv_state, zeros at position 0; the step's last taps - 1 projected rows are left there:
+ * fp32 [2, slots, taps - 1, channels], double-buffered by the sequence's parity), turns the first rot_dims dimensions
+ * of every head of q and k by position * inv_freq[i] (pairs i, i + rot_dims / 2; cos and sin times rot_mag), and writes
+ * q (`dtype` [n_tokens, heads dim]) and kv (`dtype` [n_tokens, kv_heads (dim + vdim)]: rotated keys, then values; with
+ * values_are_keys the values are the keys before the rotation and vdim = dim). */
+int umbs_attention_prep(int dtype, const float* proj, int64_t ld, const float* bias, const umbs_batch_t* batch, int heads,
+                        int kv_heads, int dim, int vdim, int values_are_keys, int taps, const float* conv_w,
+                        float* conv_state, int slots, int rot_dims, const float* inv_freq, float rot_mag, void* q, void* kv,
+                        umbs_stream_t stream);
+
+/* Mean key | mean value of every block of `pool` tokens that this step completes -> pool_cache row b of the slot.
+ * Tokens of the step come from kv, older ones of the block from the slot's rows in kv_cache (which umbs_ring_append
+ * fills: the step's kv rows, position p at row p mod kv_len). */
+int umbs_kv_pool(int dtype, const void* kv, const void* kv_cache, int kv_len, void* pool_cache, int pool_len,
+                 const umbs_batch_t* batch, int row, int pool, umbs_stream_t stream);
+
+/* Attention of a step over the step's own keys and the slot's cache.  The row at position i sees the tokens j with
+ * 0 <= i - j < window (window <= 0: every j <= i) and, with pool > 0, block b's mean key and value for every block with
+ * b pool + pool - 1 <= i - window.  Tokens j >= seq_pos0 are read from kv, older ones from kv_cache, blocks from pool_cache.
+ * mode: UMBS_ATTN_*; scores (q . k) scale (+ head_bias[h] for the sigmoid), fp32 throughout.  The output of head h is
+ * multiplied by sigmoid(gate[t ldg + h]) (gate_per_head) or element by element by sigmoid(gate[t ldg + h vdim + c]);
+ * gate may be NULL.  out: `dtype` [n_tokens, heads vdim].  dim, vdim <= 128 (umbs_window_attention_fits).
+ * split_scratch (optional, fp32): a decode step (one token per sequence) spreads every row's keys over several blocks
+ * and merges their partial sums; it needs n_tokens heads n (vdim + 2) floats there and runs unsplit with less. */
+int umbs_cached_attention(int dtype, int mode, const void* q, const void* kv, const void* kv_cache, int kv_len,
+                          const void* pool_cache, int pool_len, const umbs_batch_t* batch, int heads, int kv_heads, int dim,
+                          int vdim, int window, int pool, float scale, const float* head_bias, const float* gate, int64_t ldg,
+                          int gate_per_head, float* split_scratch, size_t split_bytes, void* out, umbs_stream_t stream);
+
+/* mLSTM over proj = [q | k | v | gate (heads vdim) | i (heads) | f (heads)] (fp32 [n_tokens, ld]); gate_bias: fp32
+ * [2 heads] for i | f.  Per head, with the log gates i = cap tanh(i' / cap), f = logsigmoid(cap tanh(f' / cap)):
+ * m_t = max(f + m_(t-1), i), S_t = e^(f + m_(t-1) - m_t) S_(t-1) + e^(i - m_t) k v^T, n_t likewise with k alone,
+ * o = S_t^T (q dim^-1/2) / (max(|n_t . q dim^-1/2|, e^(-m_t)) + 1e-6); then o / rms(o) per head (eps inside the root)
+ * times out_norm_w times sigmoid(gate) -> out (`dtype` [n_tokens, heads vdim]).  state: fp32 [slots, heads,
+ * dim (vdim + 1) + 1] (S with n as its last column, then m; read as zero at position 0).  gates_scratch: fp32
+ * [n_tokens, heads, 3]; o_scratch: fp32 [n_tokens, heads, vdim + 1]. */
+int umbs_mlstm(int dtype, const float* proj, int64_t ld, const float* gate_bias, const umbs_batch_t* batch, int heads,
+               int dim, int vdim, float gate_cap, float eps, const float* out_norm_w, float* state, float* gates_scratch,
+               float* o_scratch, void* out, umbs_stream_t stream);
 
 int umbs_embedding(int dtype, const int32_t* ids, const void* table, float* y, int n, int width, umbs_stream_t stream);
 

@@ -16,7 +16,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libumbrella_b200_seq.so")
 
 UMBS_BF16, UMBS_F32 = 0, 1
-UMBS_MIX_RETENTION, UMBS_MIX_LATENT_ATTENTION = 0, 1
+UMBS_MIX_RETENTION, UMBS_MIX_LATENT_ATTENTION, UMBS_MIX_CACHED_ATTENTION, UMBS_MIX_MLSTM = 0, 1, 2, 3
+UMBS_FORM_PARALLEL, UMBS_FORM_PRENORM = 0, 1
+UMBS_ACT_CLAMPED_GLU, UMBS_ACT_GELU_TANH = 1, 2
+UMBS_ATTN_SOFTMAX, UMBS_ATTN_SOFTMAX_SINK, UMBS_ATTN_SIGMOID = 0, 1, 2
 
 
 class Batch(C.Structure):
@@ -29,7 +32,7 @@ class Batch(C.Structure):
 class Mlp(C.Structure):
     _fields_ = [("experts", c_int), ("top", c_int), ("ff", c_int), ("limit", c_float), ("w_router", c_void_p),
                 ("w_gu", c_void_p), ("w_down", c_void_p), ("shared_ff", c_int), ("shared_limit", c_float),
-                ("ws_gu", c_void_p), ("ws_down", c_void_p)]
+                ("ws_gu", c_void_p), ("ws_down", c_void_p), ("act", c_int)]
 
 
 class Layer(C.Structure):
@@ -39,13 +42,18 @@ class Layer(C.Structure):
                 ("q_norm", c_void_p), ("kv_norm", c_void_p), ("w_uq", c_void_p), ("w_ukT", c_void_p), ("w_uv", c_void_p),
                 ("w_ukv", c_void_p), ("ring", c_void_p),
                 ("w_in", c_void_p), ("w_o", c_void_p), ("norm_w", c_void_p), ("shift_w", c_void_p),
-                ("shift_state", c_void_p), ("depth_w", c_void_p), ("has_mlp", c_int), ("mlp", Mlp)]
+                ("shift_state", c_void_p), ("depth_w", c_void_p), ("has_mlp", c_int), ("mlp", Mlp),
+                ("form", c_int), ("norm_offset", c_float), ("norm2_w", c_void_p),
+                ("kv_heads", c_int), ("attn_mode", c_int), ("gate_kind", c_int), ("values_are_keys", c_int), ("pool", c_int),
+                ("taps", c_int), ("rot_mag", c_float), ("gate_cap", c_float), ("bias_in", c_void_p), ("conv_w", c_void_p),
+                ("head_bias", c_void_p), ("out_norm_w", c_void_p), ("kv_cache", c_void_p), ("kv_len", c_int),
+                ("pool_cache", c_void_p), ("pool_len", c_int), ("conv_state", c_void_p), ("mlstm_state", c_void_p)]
 
 
 class Model(C.Structure):
     _fields_ = [("dtype", c_int), ("width", c_int), ("vocab", c_int), ("n_layers", c_int), ("norm_groups", c_int),
                 ("slots", c_int), ("norm_eps", c_float), ("embed", c_void_p), ("final_norm", c_void_p), ("head", c_void_p),
-                ("layers", C.POINTER(Layer))]
+                ("layers", C.POINTER(Layer)), ("norm_offset", c_float), ("logit_softcap", c_float)]
 
 
 _BP = C.POINTER(Batch)
@@ -74,6 +82,17 @@ SIGNATURES = {
                                c_void_p, c_void_p, c_void_p]),
     "umbs_depth_mix": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "umbs_add_rms_norm": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_float, c_void_p,
+                                  c_void_p, c_void_p]),
+    "umbs_softcap": (c_int, [c_void_p, c_int64, c_float, c_void_p]),
+    "umbs_attention_prep": (c_int, [c_int, c_void_p, c_int64, c_void_p, _BP, c_int, c_int, c_int, c_int, c_int, c_int,
+                                    c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p]),
+    "umbs_kv_pool": (c_int, [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, _BP, c_int, c_int, c_void_p]),
+    "umbs_cached_attention": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, _BP, c_int, c_int,
+                                      c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int64, c_int, c_void_p,
+                                      c_size_t, c_void_p, c_void_p]),
+    "umbs_mlstm": (c_int, [c_int, c_void_p, c_int64, c_void_p, _BP, c_int, c_int, c_int, c_float, c_float, c_void_p,
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "umbs_embedding": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
 }
 

@@ -1,12 +1,19 @@
 """Slot-based state of the sequence-state decoders (the counterpart of attn/cache.py's KV_Cache for models whose
-per-sequence memory does not grow with the context).
+per-sequence memory is mostly a fixed-size state).
 
 Every live sequence owns one slot.  A slot holds, per layer,
   * token shift: the previous token's normed activations, fp32 [width], double-buffered (a step reads the half
     ``parity`` names and writes the other, then the parity flips);
   * retention layers: the state matrices, fp32 [heads, dim, vdim];
   * latent-attention layers: a ring of the last ``ring_len`` latents, [ring_len, kv_rank] in the activation dtype,
-    position p at row p mod ring_len (ring_len = the layer's window, capped by ``max_length`` when that is given).
+    position p at row p mod ring_len (ring_len = the layer's window, capped by ``max_length`` when that is given);
+  * cached-attention layers: key | value rows per token, [kv_len, kv_heads (dim + vdim)] in the activation dtype,
+    position p at row p mod kv_len -- with a window a ring of max(window, pool) rows, without one a row for every
+    token up to ``capacity`` tokens (the cache reallocates with twice the capacity when a sequence outgrows it);
+    with pooled blocks a table of one mean key | value row per block, [capacity / pool, .]; with a short convolution
+    the last taps - 1 projected q | k rows, fp32, double-buffered like the shift state;
+  * mLSTM layers: per head the matrix S with the normaliser n as one more column and the running maximum m,
+    fp32 [heads, dim (vdim + 1) + 1].
 and on the host its position (tokens fed so far) and parity.  Nothing is cleared when a slot is freed or handed out
 again: the kernels read a sequence's state as zero while its position is 0, and a ring row is only ever read for a
 position that the current owner has written.
@@ -17,10 +24,18 @@ import torch
 
 
 class SequenceStateCache:
-    def __init__(self, spec, slots: int = 8, device="cuda:0", dtype=torch.bfloat16, max_length: int | None = None):
+    def __init__(self, spec, slots: int = 8, device="cuda:0", dtype=torch.bfloat16, max_length: int | None = None,
+                 capacity: int = 0):
         self.spec, self.device, self.dtype = spec, torch.device(device), dtype
         self.max_length = max_length
         self.slots = 0
+        # tokens per sequence that the growing parts (windowless key/value rows, pooled-block tables) hold
+        self.capacity = int(max_length or capacity or 512)
+        n = len(spec.layers)
+        self.kv_cache: list[torch.Tensor | None] = [None] * n
+        self.pool_cache: list[torch.Tensor | None] = [None] * n
+        self.conv_state: list[torch.Tensor | None] = [None] * n
+        self.mlstm_state: list[torch.Tensor | None] = [None] * n
         self.shift: list[torch.Tensor | None] = [None] * len(spec.layers)
         self.ret_state: list[torch.Tensor | None] = [None] * len(spec.layers)
         self.ring: list[torch.Tensor | None] = [None] * len(spec.layers)
@@ -34,18 +49,43 @@ class SequenceStateCache:
         n = int(layer.window)
         return max(1, min(n, self.max_length) if self.max_length else n)
 
+    def kv_len(self, layer) -> int:
+        """Rows of a cached-attention layer's key/value cache per slot."""
+        return max(int(layer.window), int(layer.pool), 1) if layer.window > 0 else self.capacity
+
+    def pool_len(self, layer) -> int:
+        return max(1, -(-self.capacity // int(layer.pool))) if layer.pool > 0 else 0
+
+    def reserve_length(self, tokens: int):
+        """Make sure a sequence of ``tokens`` tokens fits the growing parts (doubling the capacity when it does not)."""
+        if tokens <= self.capacity:
+            return
+        if self.max_length is not None and tokens > self.max_length:
+            raise RuntimeError(f"sequence longer than max_length {self.max_length}")
+        cap = self.capacity
+        while cap < tokens:
+            cap *= 2
+        self._resize(self.slots, min(cap, self.max_length) if self.max_length else cap)
+
     def grow(self, slots: int):
         """Make room for ``slots`` slots, keeping what the existing ones hold."""
-        if slots <= self.slots:
-            return
+        if slots > self.slots:
+            self._resize(slots, self.capacity)
+
+    def _resize(self, slots: int, capacity: int):
         old = self.slots
         f32 = dict(dtype=torch.float32, device=self.device)
+        act = dict(dtype=self.dtype, device=self.device)
 
         def widen(t_old, shape, slot_dim, **kw):
             t = torch.zeros(shape, **kw)
             if t_old is not None:
-                t.narrow(slot_dim, 0, old).copy_(t_old)
+                part = t.narrow(slot_dim, 0, old)
+                if part.shape != t_old.shape:                       # a longer cache: rows keep their index
+                    part = part.narrow(slot_dim + 1, 0, t_old.shape[slot_dim + 1])
+                part.copy_(t_old)
             return t
+        self.capacity = capacity
         for i, l in enumerate(self.spec.layers):
             if l.shift:
                 self.shift[i] = widen(self.shift[i], (2, slots, self.spec.width), 1, **f32)
@@ -54,6 +94,16 @@ class SequenceStateCache:
             elif l.mixer == "latent_attention":
                 self.ring[i] = widen(self.ring[i], (slots, self.ring_len(l), l.kv_rank), 0, dtype=self.dtype,
                                      device=self.device)
+            elif l.mixer == "cached_attention":
+                row = l.kv_heads * (l.dim + l.vdim)
+                self.kv_cache[i] = widen(self.kv_cache[i], (slots, self.kv_len(l), row), 0, **act)
+                if l.pool > 0:
+                    self.pool_cache[i] = widen(self.pool_cache[i], (slots, self.pool_len(l), row), 0, **act)
+                if l.taps > 1:
+                    self.conv_state[i] = widen(self.conv_state[i], (2, slots, l.taps - 1, (l.heads + l.kv_heads) * l.dim),
+                                               1, **f32)
+            elif l.mixer == "mlstm":
+                self.mlstm_state[i] = widen(self.mlstm_state[i], (slots, l.heads, l.dim * (l.vdim + 1) + 1), 0, **f32)
         self.position += [0] * (slots - old)
         self.parity += [0] * (slots - old)
         self._free += list(range(old, slots))
@@ -84,7 +134,7 @@ class SequenceStateCache:
 
     def state_bytes_per_slot(self) -> int:
         n = 0
-        for t in self.shift + self.ret_state + self.ring:
+        for t in self.shift + self.ret_state + self.ring + self.kv_cache + self.pool_cache + self.conv_state + self.mlstm_state:
             if t is not None:
                 n += t.numel() * t.element_size() // self.slots
         return n

@@ -51,17 +51,31 @@ struct Scratch {
     void* ys;          // act [T, max shared ff]
     float* shared_out; // fp32 [T, width]
     void* final_h;     // act [n_want, width]
+    float* gates;      // fp32 [T, max heads, 3]           mlstm: decay, input weight, floor per (token, head)
+    float* ca_part;    // fp32 key-split partial sums of cached attention in decode steps
+    size_t ca_part_bytes;
 };
 
 static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratch* s) {
     const size_t es = m->dtype == UMBS_F32 ? 4 : 2;
     size_t segb = 0;
     int hmax = 1, rotd = 1, in_rows = 1, hv = 1, qr = 1, kvr = 1, hd = 1, hkv = 1, hkvw = 1, top = 1, experts = 1, ff = 1, sff = 1;
+    int hall = 1, cav = 1;
+    bool parallel = false;
     for (int i = 0; i < m->n_layers; ++i) {
         const umbs_layer_t& l = m->layers[i];
         auto up = [](int& a, int b) { if (b > a) a = b; };
         up(hv, l.heads * l.vdim);
-        if (l.mixer == UMBS_MIX_RETENTION) {
+        up(hall, l.heads);
+        if (l.form == UMBS_FORM_PARALLEL) parallel = true;
+        if (l.mixer == UMBS_MIX_CACHED_ATTENTION) {
+            const int gate_rows = l.gate_kind == 1 ? l.heads : (l.gate_kind == 2 ? l.heads * l.vdim : 0);
+            up(in_rows, l.heads * l.dim + l.kv_heads * l.dim + (l.values_are_keys ? 0 : l.kv_heads * l.vdim) + gate_rows);
+            up(hd, l.heads * l.dim); up(hkvw, l.kv_heads * (l.dim + l.vdim)); up(cav, l.vdim);
+        } else if (l.mixer == UMBS_MIX_MLSTM) {
+            up(in_rows, 2 * l.heads * l.dim + 2 * l.heads * l.vdim + 2 * l.heads);
+            up(hv, l.heads * (l.vdim + 1));                        // o32 holds n . q as one more column per head
+        } else if (l.mixer == UMBS_MIX_RETENTION) {
             up(in_rows, 2 * l.heads * l.dim + 2 * l.heads * l.vdim); up(rotd, l.rot_dims);
             // segment states of a step of few long sequences: about 592 blocks' worth (umbs_retention uses what fits)
             const size_t plane = (size_t)l.heads * l.dim * l.vdim * 4, ent = 592 / ((size_t)l.heads * ((l.vdim + 31) / 32)) + 8;
@@ -77,7 +91,7 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
     Arena a{base, 0, 0};
     const size_t W = m->width, Tz = T;
     Scratch z;
-    z.stack = (float*)a.take((size_t)(m->n_layers + 1) * Tz * W * 4);
+    z.stack = (float*)a.take((size_t)(parallel ? m->n_layers + 1 : 1) * Tz * W * 4);   // pre-norm layers keep one residual stream
     z.x = (float*)a.take(Tz * W * 4);
     z.h = a.take(Tz * W * es);
     z.hs = a.take(Tz * W * es);
@@ -106,6 +120,9 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
     z.ys = a.take(Tz * sff * es);
     z.shared_out = (float*)a.take(Tz * W * 4);
     z.final_h = a.take((size_t)(n_want > 0 ? n_want : 1) * W * es);
+    z.gates = (float*)a.take(Tz * hall * 3 * 4);
+    z.ca_part_bytes = (size_t)2048 * ((size_t)cav + 2) * 4;                 // (token, head, split) triples of a decode step
+    z.ca_part = (float*)a.take(z.ca_part_bytes);
     if (s) *s = z;
     return a.used + 256;
 }
@@ -134,6 +151,71 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
     const int64_t plane = (int64_t)T * W;
     UMBS_TRY(umbs_embedding(dt, b->tok_ids, m->embed, s.stack, T, W, stream));
     const float* x = s.stack;                    // layer 0 reads X_0 itself
+    bool prenorm = false;
+    for (int i = 0; i < m->n_layers; ++i) {
+        if (i > 0 && m->layers[i].form != m->layers[0].form) return UMB_ERR_UNSUPPORTED;    // one form per model
+        prenorm = m->layers[i].form == UMBS_FORM_PRENORM;
+    }
+    // Pre-norm layers: one fp32 residual stream, updated in place.  Every block's output waits in `pending` and is added
+    // by the kernel that computes the next norm (or, behind the last layer, by the final norm).
+    const float* pending = nullptr;
+    for (int i = 0; prenorm && i < m->n_layers; ++i) {
+        const umbs_layer_t& l = m->layers[i];
+        const int hv = l.heads * l.vdim;
+        UMBS_TRY(umbs_add_rms_norm(dt, s.stack, pending, nullptr, T, l.norm_w, l.norm_offset, W, m->norm_eps, s.h,
+                                   (layer_out && i > 0) ? layer_out + (int64_t)(i - 1) * plane : nullptr, stream));
+        if (l.mixer == UMBS_MIX_CACHED_ATTENTION) {
+            const int cq = l.heads * l.dim, ck = l.kv_heads * l.dim, cv = l.values_are_keys ? 0 : l.kv_heads * l.vdim;
+            const int gate_rows = l.gate_kind == 1 ? l.heads : (l.gate_kind == 2 ? hv : 0);
+            const int rows = cq + ck + cv + gate_rows, row_kv = l.kv_heads * (l.dim + l.vdim);
+            UMBS_TRY(umbs_gemm(dt, s.h, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
+            UMBS_TRY(umbs_attention_prep(dt, s.proj, rows, l.bias_in, b, l.heads, l.kv_heads, l.dim, l.vdim, l.values_are_keys,
+                                         l.taps, l.conv_w, l.conv_state, m->slots, l.rot_dims, l.inv_freq, l.rot_mag, s.q, s.kv,
+                                         stream));
+            if (l.pool > 0)
+                UMBS_TRY(umbs_kv_pool(dt, s.kv, l.kv_cache, l.kv_len, l.pool_cache, l.pool_len, b, row_kv, l.pool, stream));
+            UMBS_TRY(umbs_cached_attention(dt, l.attn_mode, s.q, s.kv, l.kv_cache, l.kv_len, l.pool_cache, l.pool_len, b, l.heads,
+                                           l.kv_heads, l.dim, l.vdim, l.window, l.pool, l.scale, l.head_bias,
+                                           gate_rows ? s.proj + cq + ck + cv : nullptr, rows, l.gate_kind == 1, s.ca_part,
+                                           s.ca_part_bytes, s.mixed, stream));
+            UMBS_TRY(umbs_ring_append(dt, s.kv, l.kv_cache, l.kv_len, b, row_kv, stream));
+        } else if (l.mixer == UMBS_MIX_MLSTM) {
+            const int rows = 2 * l.heads * l.dim + 2 * hv + 2 * l.heads;
+            UMBS_TRY(umbs_gemm(dt, s.h, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
+            UMBS_TRY(umbs_mlstm(dt, s.proj, rows, l.bias_in, b, l.heads, l.dim, l.vdim, l.gate_cap, m->norm_eps, l.out_norm_w,
+                                l.mlstm_state, s.gates, s.o32, s.mixed, stream));
+        } else {
+            return UMB_ERR_UNSUPPORTED;
+        }
+        UMBS_TRY(umbs_gemm(dt, s.mixed, hv, 0, l.w_o, hv, 0, s.mix_out, W, 0, 1, T, W, hv, 1, nullptr, nullptr, 0, 0.f, stream));
+        pending = s.mix_out;
+        if (l.has_mlp) {
+            const umbs_mlp_t& f = l.mlp;
+            if (f.experts > 0 || f.shared_ff <= 0 || l.norm2_w == nullptr) return UMB_ERR_UNSUPPORTED;   // dense feed-forward only
+            UMBS_TRY(umbs_add_rms_norm(dt, s.stack, pending, nullptr, T, l.norm2_w, l.norm_offset, W, m->norm_eps, s.h, nullptr,
+                                       stream));
+            UMBS_TRY(umbs_gemm(dt, s.h, W, 0, f.ws_gu, W, 0, s.ys, f.shared_ff, 0, 0, T, f.shared_ff, W, 1, nullptr, nullptr,
+                               f.act ? f.act : UMBS_ACT_CLAMPED_GLU, f.shared_limit, stream));
+            UMBS_TRY(umbs_gemm(dt, s.ys, f.shared_ff, 0, f.ws_down, f.shared_ff, 0, s.shared_out, W, 0, 1, T, W, f.shared_ff, 1,
+                               nullptr, nullptr, 0, 0.f, stream));
+            pending = s.shared_out;
+        }
+    }
+    if (prenorm) {
+        if (layer_out != nullptr) {              // the last layer's stream is asked for: finish the sum for every row
+            UMBS_TRY(umbs_add_rms_norm(dt, s.stack, pending, nullptr, T, nullptr, 0.f, W, m->norm_eps, nullptr,
+                                       layer_out + (int64_t)(m->n_layers - 1) * plane, stream));
+            pending = nullptr;
+        }
+        if (logits != nullptr && b->n_want > 0) {
+            UMBS_TRY(umbs_add_rms_norm(dt, s.stack, pending, b->want_rows, b->n_want, m->final_norm, m->norm_offset, W,
+                                       m->norm_eps, s.final_h, nullptr, stream));
+            UMBS_TRY(umbs_gemm(dt, s.final_h, W, 0, m->head, W, 0, logits, m->vocab, 0, 1, b->n_want, m->vocab, W, 1, nullptr,
+                               nullptr, 0, 0.f, stream));
+            if (m->logit_softcap > 0.f) UMBS_TRY(umbs_softcap(logits, (int64_t)b->n_want * m->vocab, m->logit_softcap, stream));
+        }
+        return 0;
+    }
     for (int i = 0; i < m->n_layers; ++i) {
         const umbs_layer_t& l = m->layers[i];
         UMBS_TRY(umbs_group_norm_shift(dt, x, l.norm_w, l.shift_w, l.shift_state, m->slots, b, W, m->norm_groups,
@@ -206,6 +288,7 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
                                       stream));
         UMBS_TRY(umbs_gemm(dt, s.final_h, W, 0, m->head, W, 0, logits, m->vocab, 0, 1, b->n_want, m->vocab, W, 1, nullptr, nullptr, 0,
                            0.f, stream));
+        if (m->logit_softcap > 0.f) UMBS_TRY(umbs_softcap(logits, (int64_t)b->n_want * m->vocab, m->logit_softcap, stream));
     }
     return 0;
 }

@@ -26,9 +26,14 @@ struct GemmArgs {
     const int32_t* grp_off;
     const int32_t* row_src;
     float limit;
+    int act;          // UMBS_ACT_*: which gated activation a dual product applies
 };
 
-__device__ __forceinline__ float gated_act(float g, float u, float limit) {
+__device__ __forceinline__ float gated_act(float g, float u, float limit, int act) {
+    if (act == UMBS_ACT_GELU_TANH) {      // 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * u
+        const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        return 0.5f * g * (1.f + tanhf(z)) * u;
+    }
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
     return g * (1.f / (1.f + expf(-1.702f * g))) * (u + 1.f);
@@ -95,7 +100,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(GemmArgs a) {
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= a.N) continue;
-            const float v = DUAL ? gated_act(acc[i][j], acc2[DUAL ? i : 0][j], a.limit) : acc[i][j];
+            const float v = DUAL ? gated_act(acc[i][j], acc2[DUAL ? i : 0][j], a.limit, a.act) : acc[i][j];
             C[(int64_t)(row_lo + m) * a.ldc + n] = from_f32<TC>(v);
         }
     }
@@ -206,7 +211,7 @@ __global__ void __launch_bounds__(256) gemm_mma_kernel(GemmArgs a) {
             for (int e = 0; e < 4; ++e) {
                 const int m = m0 + wm + 16 * i + gr + (e >> 1) * 8, n = n0 + wn + 8 * j + gc + (e & 1);
                 if (m >= rows || n >= a.N) continue;
-                const float v = DUAL ? gated_act(acc[i][j][e], acc2[DUAL ? i : 0][j][e], a.limit) : acc[i][j][e];
+                const float v = DUAL ? gated_act(acc[i][j][e], acc2[DUAL ? i : 0][j][e], a.limit, a.act) : acc[i][j][e];
                 C[(int64_t)(row_lo + m) * a.ldc + n] = from_f32<TC>(v);
             }
 }
@@ -286,7 +291,7 @@ __global__ void __launch_bounds__(32 * SK_WARPS) gemm_skinny_kernel(GemmArgs a) 
 #pragma unroll
             for (int m = 0; m < MT; ++m) {
                 if (m0 + m >= rows) continue;
-                const float v = DUAL ? gated_act(acc[2 * o][m], acc[DUAL ? 2 * o + 1 : o][m], a.limit) : acc[o][m];
+                const float v = DUAL ? gated_act(acc[2 * o][m], acc[DUAL ? 2 * o + 1 : o][m], a.limit, a.act) : acc[o][m];
                 C[(int64_t)(row_lo + m0 + m) * a.ldc + n0 + o] = from_f32<TC>(v);
             }
         }
@@ -333,7 +338,8 @@ extern "C" int umbs_gemm(int dtype, const void* A, int64_t lda, int a_goff, cons
     if (M <= 0 || N <= 0 || groups <= 0) return 0;
     if (K <= 0 || A == nullptr || W == nullptr || C == nullptr) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    GemmArgs a{A, lda, a_goff, W, ldw, w_gstride, C, ldc, c_goff, M, N, K, grp_off, row_src, limit};
+    GemmArgs a{A, lda, a_goff, W, ldw, w_gstride, C, ldc, c_goff, M, N, K, grp_off, row_src, limit,
+               dual == UMBS_ACT_GELU_TANH ? UMBS_ACT_GELU_TANH : UMBS_ACT_CLAMPED_GLU};
     if (dtype == UMBS_F32) {
         launch_simt<float, float>(a, groups, dual != 0, st);          // activations are fp32 too: c_f32 changes nothing
     } else if (dtype == UMBS_BF16) {

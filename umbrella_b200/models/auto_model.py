@@ -49,8 +49,13 @@ def _radanex(path, **kw):
     return radanex.from_pretrained(path, **kw)
 
 
+def _zedotar(path, **kw):
+    from . import zedotar
+    return zedotar.from_pretrained(path, **kw)
+
+
 # config.json ``architecture`` -> factory(path, device=, dtype=, max_length=, slots=, max_tokens=, ...)
-_ARCHITECTURES = {"Radanex": _radanex}
+_ARCHITECTURES = {"Radanex": _radanex, "Zedotar": _zedotar}
 
 
 def _make(model_name, offload=False, batch_size=1, max_length=None, device="cuda:0", dtype=torch.float16, **unused):

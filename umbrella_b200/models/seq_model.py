@@ -1,10 +1,12 @@
 """Sequence-state decoders on the native batched step (umbs_forward of libumbrella_b200_seq.so).
 
-A model is a ``SeqModelSpec``: width, vocabulary, the grouped RMS norm's constants and a list of ``SeqLayerSpec``s,
-each naming its mixer (``"retention"`` or ``"latent_attention"``) with that mixer's sizes and constants, whether it
-has token shift and a depth average, and its feed-forward (routed experts and / or a shared expert, or none).  Model
-families (models/radanex.py) translate their config.json into a spec and their tensors into the per-layer weight
-dicts ``load_layer`` takes; nothing below knows a family's names.
+A model is a ``SeqModelSpec``: width, vocabulary, the norm's constants and a list of ``SeqLayerSpec``s, each naming
+its form (``"parallel"``: one grouped norm feeds mixer and feed-forward side by side, with token shift and a depth
+average as options; ``"prenorm"``: x += mixer(norm1(x)), x += ff(norm2(x))), its mixer (``"retention"``,
+``"latent_attention"``, ``"cached_attention"`` or ``"mlstm"``) with that mixer's sizes and constants, and its
+feed-forward (routed experts and / or a shared expert -- a dense feed-forward is a shared expert alone -- or none).
+Model families (models/radanex.py, models/zedotar.py) translate their config.json into a spec and their tensors into
+the per-layer weight dicts ``load_layer`` takes; nothing below knows a family's names.
 
 One ``forward`` call runs a ragged batch: for every sequence its slot of the ``SequenceStateCache`` and its next
 tokens (any number: a whole prompt, a portion of one, one decoded token), and the places whose logits are wanted.
@@ -13,6 +15,7 @@ The batch description goes host -> device in one pinned copy; one C call enqueue
 from __future__ import annotations
 
 import ctypes as C
+import math
 from dataclasses import dataclass, field
 
 import torch
@@ -29,6 +32,7 @@ class SeqMlpSpec:
     limit: float = 0.0
     shared_ff: int = 0
     shared_limit: float = 0.0
+    act: str = "clamped_glu"          # or "gelu_tanh"
 
 
 @dataclass
@@ -46,7 +50,22 @@ class SeqLayerSpec:
     kv_rank: int = 0
     window: int = 0
     scale: float = 1.0
+    # cached attention (also: rot_dims, window (0 = every earlier token), scale)
+    kv_heads: int = 0
+    attn_mode: str = "softmax"        # "softmax" | "softmax_sink" | "sigmoid"
+    gate_kind: int = 0                # 0 none, 1 one sigmoid gate per head, 2 one per output element
+    values_are_keys: bool = False     # values = keys before the rotation (no value projection)
+    pool: int = 0                     # tokens per pooled block of keys that have left the window
+    taps: int = 1                     # short causal convolution on q and k
+    bias: bool = False                # q, k, v projections carry biases
+    head_bias: bool = False           # a number per head added to the scores
+    inv_freq: list | None = None      # rotary frequencies when they are not base^(-2i/rot_dims) (scaled forms)
+    rot_mag: float = 1.0              # factor on cos and sin
+    # mlstm
+    gate_cap: float = 0.0
     # layer
+    form: str = "parallel"
+    norm_offset: float = 0.0          # added to the layer's norm weights (1: weights stored around zero)
     shift: bool = True
     depth_average: bool = True
     mlp: SeqMlpSpec | None = None
@@ -59,6 +78,8 @@ class SeqModelSpec:
     layers: list
     norm_groups: int = 1
     norm_eps: float = 1e-6
+    norm_offset: float = 0.0          # added to the final norm's weight
+    logit_softcap: float = 0.0        # > 0: logits <- cap tanh(logits / cap)
     eos_token_id: list = field(default_factory=list)
 
     # compatibility with the engines' view of a config
@@ -75,6 +96,39 @@ def rotary_inv_freq(rot_dims: int, base: float) -> torch.Tensor:
     """f_i = base^(-2 i / rot_dims), i < rot_dims / 2: evaluated in double, rounded once to fp32."""
     i = torch.arange(rot_dims // 2, dtype=torch.float64)
     return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / rot_dims).to(torch.float32)
+
+
+def scale_freq_by_wavelength(f: torch.Tensor, factor: float, low: float, high: float, original: float) -> torch.Tensor:
+    """Frequency scaling by wavelength l = 2 pi / f against an original context length: kept where l < original / high,
+    divided by ``factor`` where l > original / low, blended in between with s = (original / l - low) / (high - low).
+    float64 in, float64 out."""
+    wave = 2.0 * math.pi / f
+    s = ((original / wave - low) / (high - low)).clamp(0.0, 1.0)
+    mid = (1.0 - s) * f / factor + s * f
+    return torch.where(wave < original / high, f, torch.where(wave > original / low, f / factor, mid))
+
+
+def scale_freq_yarn(f: torch.Tensor, rot_dims: int, base: float, factor: float, original: float, fast: float,
+                    slow: float) -> tuple[torch.Tensor, float]:
+    """YaRN: frequencies that turn more than ``fast`` times over the original context are kept, those that turn less
+    than ``slow`` times are divided by ``factor``, a linear ramp over the dimension index in between; cos and sin are
+    scaled by 0.1 ln(factor) + 1.  -> (frequencies, that factor)."""
+    turn = lambda t: rot_dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(base))
+    lo, hi = max(math.floor(turn(fast)), 0), min(math.ceil(turn(slow)), rot_dims - 1)
+    i = torch.arange(f.numel(), dtype=torch.float64)
+    ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+def rotary_inv_freq64(rot_dims: int, base: float) -> torch.Tensor:
+    i = torch.arange(rot_dims // 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / rot_dims)
+
+
+_MIXERS = {"retention": S.UMBS_MIX_RETENTION, "latent_attention": S.UMBS_MIX_LATENT_ATTENTION,
+           "cached_attention": S.UMBS_MIX_CACHED_ATTENTION, "mlstm": S.UMBS_MIX_MLSTM}
+_ATTN_MODES = {"softmax": S.UMBS_ATTN_SOFTMAX, "softmax_sink": S.UMBS_ATTN_SOFTMAX_SINK, "sigmoid": S.UMBS_ATTN_SIGMOID}
+_ACTS = {"clamped_glu": S.UMBS_ACT_CLAMPED_GLU, "gelu_tanh": S.UMBS_ACT_GELU_TANH}
 
 
 class SeqStateModel:
@@ -115,7 +169,7 @@ class SeqStateModel:
         if self.device.type != "cuda":
             raise RuntimeError("sequence-state decoders need a CUDA device (there is no CPU path)")
         self.cache = SequenceStateCache(self.spec, slots=kwargs.get("slots", self._slots0), device=self.device,
-                                        dtype=self.dtype, max_length=self.max_length)
+                                        dtype=self.dtype, max_length=self.max_length, capacity=self._max_tokens0)
         return self
 
     def _reserve(self, tokens: int, want: int):
@@ -147,6 +201,10 @@ class SeqStateModel:
         feed-forward: router [experts, width]; experts: list of (gate, up, down); shared: (gate, up, down)."""
         l = self.spec.layers[idx]
         d = dict(norm=self._f32(w["norm"]), o=self._act(w["o"]))
+        if l.form == "prenorm":
+            l.shift = l.depth_average = False
+            if l.mlp is not None:
+                d["norm2"] = self._f32(w["norm2"])
         if l.shift:
             d["shift"] = self._f32(w["shift"])
         if l.depth_average:
@@ -168,6 +226,32 @@ class SeqStateModel:
             # key rows then value rows in one matrix: a step of fresh sequences up-projects its latents with one product
             d["ukv"] = self._act(torch.cat([w["uk"], w["uv"]], dim=0))
             assert d["uq"].shape == (l.heads * l.dim, l.q_rank) and d["uv"].shape == (l.heads * l.vdim, l.kv_rank)
+        elif l.mixer == "cached_attention":
+            # in-projection rows: q | k | v (unless the values are the keys) | gate; biases for q | k | v in the same order
+            cq, ck = l.heads * l.dim, l.kv_heads * l.dim
+            parts = [w["q"], w["k"]] + ([] if l.values_are_keys else [w["v"]]) + ([w["g"]] if l.gate_kind else [])
+            d["w_in"] = self._act(torch.cat(parts, dim=0))
+            assert w["q"].shape[0] == cq and w["k"].shape[0] == ck and l.heads % l.kv_heads == 0
+            assert not l.gate_kind or w["g"].shape[0] == (l.heads if l.gate_kind == 1 else l.heads * l.vdim)
+            assert not l.values_are_keys or l.vdim == l.dim
+            if l.bias:
+                d["bias_in"] = self._f32(torch.cat([w["q_b"], w["k_b"]] + ([] if l.values_are_keys else [w["v_b"]])))
+            if l.taps > 1:
+                d["conv_w"] = self._f32(torch.cat([w["q_conv"], w["k_conv"]], dim=0))
+                assert d["conv_w"].shape == (cq + ck, l.taps)
+            if l.head_bias:
+                d["head_bias"] = self._f32(w["pb"])
+            f = torch.tensor(l.inv_freq, dtype=torch.float64) if l.inv_freq is not None else \
+                rotary_inv_freq64(l.rot_dims, l.rot_base)
+            d["inv_freq"] = f.to(torch.float32).to(self.device) if l.rot_dims else \
+                torch.zeros(1, dtype=torch.float32, device=self.device)
+            assert l.rot_dims == 0 or d["inv_freq"].numel() == l.rot_dims // 2
+        elif l.mixer == "mlstm":
+            d["w_in"] = self._act(torch.cat([w["q"], w["k"], w["v"], w["g"], w["i"], w["f"]], dim=0))
+            d["bias_in"] = self._f32(torch.cat([w["i_b"], w["f_b"]]))
+            d["out_norm"] = self._f32(w["out_norm"])
+            assert d["w_in"].shape == (2 * l.heads * (l.dim + l.vdim) + 2 * l.heads, self.spec.width)
+            assert d["out_norm"].numel() == l.heads * l.vdim and l.gate_cap > 0
         else:
             raise ValueError(f"unknown mixer '{l.mixer}'")
         assert d["o"].shape == (self.spec.width, l.heads * l.vdim)
@@ -179,7 +263,7 @@ class SeqStateModel:
                 d["down"] = self._act(torch.stack([dn for _, _, dn in w["experts"]]))
                 assert d["gu"].shape == (m.experts, 2 * m.ff, self.spec.width)
             if m.shared_ff:
-                g, u, dn = w["shared"]
+                g, u, dn = w["shared"] if "shared" in w else w["dense"]
                 d["s_gu"], d["s_down"] = self._act(torch.cat([g, u], dim=0)), self._act(dn)
                 assert d["s_gu"].shape == (2 * m.shared_ff, self.spec.width)
         self.weights[idx] = d
@@ -201,11 +285,24 @@ class SeqStateModel:
         layers = (S.Layer * self.num_layers)()
         for i, (l, w) in enumerate(zip(sp.layers, self.weights)):
             cl = layers[i]
-            cl.mixer = S.UMBS_MIX_RETENTION if l.mixer == "retention" else S.UMBS_MIX_LATENT_ATTENTION
+            cl.mixer = _MIXERS[l.mixer]
             cl.heads, cl.dim, cl.vdim = l.heads, l.dim, l.vdim
+            cl.form = S.UMBS_FORM_PRENORM if l.form == "prenorm" else S.UMBS_FORM_PARALLEL
+            cl.norm_offset, cl.norm2_w = l.norm_offset, p(w.get("norm2"))
             if l.mixer == "retention":
                 cl.rot_dims, cl.inv_freq, cl.decay = l.rot_dims, p(w["inv_freq"]), p(w["decay"])
                 cl.ret_state = p(cache.ret_state[i])
+            elif l.mixer == "cached_attention":
+                cl.kv_heads, cl.attn_mode, cl.gate_kind = l.kv_heads, _ATTN_MODES[l.attn_mode], l.gate_kind
+                cl.values_are_keys, cl.pool, cl.taps, cl.window, cl.scale = int(l.values_are_keys), l.pool, l.taps, l.window, l.scale
+                cl.rot_dims, cl.inv_freq, cl.rot_mag = l.rot_dims, p(w["inv_freq"]), l.rot_mag
+                cl.bias_in, cl.conv_w, cl.head_bias = p(w.get("bias_in")), p(w.get("conv_w")), p(w.get("head_bias"))
+                cl.kv_cache, cl.kv_len = p(cache.kv_cache[i]), cache.kv_len(l)
+                cl.pool_cache, cl.pool_len = p(cache.pool_cache[i]), cache.pool_len(l)
+                cl.conv_state = p(cache.conv_state[i])
+            elif l.mixer == "mlstm":
+                cl.gate_cap, cl.bias_in, cl.out_norm_w = l.gate_cap, p(w["bias_in"]), p(w["out_norm"])
+                cl.mlstm_state = p(cache.mlstm_state[i])
             else:
                 cl.q_rank, cl.kv_rank, cl.window, cl.ring_len = l.q_rank, l.kv_rank, l.window, cache.ring_len(l)
                 cl.scale = l.scale
@@ -223,10 +320,11 @@ class SeqStateModel:
                 cl.mlp.w_router, cl.mlp.w_gu, cl.mlp.w_down = p(w.get("router")), p(w.get("gu")), p(w.get("down"))
                 cl.mlp.shared_ff, cl.mlp.shared_limit = m.shared_ff, m.shared_limit
                 cl.mlp.ws_gu, cl.mlp.ws_down = p(w.get("s_gu")), p(w.get("s_down"))
+                cl.mlp.act = _ACTS[m.act]
         m = S.Model()
         m.dtype = S.UMBS_BF16 if self.dtype == torch.bfloat16 else S.UMBS_F32
         m.width, m.vocab, m.n_layers, m.norm_groups, m.slots = sp.width, sp.vocab, self.num_layers, sp.norm_groups, cache.slots
-        m.norm_eps = sp.norm_eps
+        m.norm_eps, m.norm_offset, m.logit_softcap = sp.norm_eps, sp.norm_offset, sp.logit_softcap
         hw = self.head_weights
         m.embed, m.final_norm, m.head = p(hw["embed"]), p(hw["final_norm"]), p(hw["head"])
         m.layers = C.cast(layers, C.POINTER(S.Layer))
@@ -256,6 +354,8 @@ class SeqStateModel:
             tok_seq += [b] * n
             tok_pos += range(p0, p0 + n)
         T, B, Wn = len(ids), len(entries), len(want)
+        if T:
+            cache.reserve_length(max(p + n for p, n in zip(pos0, length)))      # growing parts: room for the longest sequence
         if T == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=self.device)
         if len(set(slot)) != B:
