@@ -110,7 +110,7 @@ def causal_conv(u, w):
 def pooled_window_attention(q, k, v, window, pool, scale):
     """q [n, H, D], k [n, G, D], v [n, G, V].  Row i sees tokens j with 0 <= i - j < window and, for every block b of
     `pool` tokens with b pool + pool - 1 <= i - window, the block's mean key and mean value.  One softmax over both,
-    with a sink of score 0 and no value: p = exp(s) / (1 + sum exp(s))."""
+    with a sink of score 0 and no value: p = exp(s) / (1 + sum exp(s)).  pool = 0: no blocks."""
     n, H, D = q.shape
     G, V = k.shape[1], v.shape[2]
     out = torch.zeros(n, H, V, dtype=F64)
@@ -119,7 +119,7 @@ def pooled_window_attention(q, k, v, window, pool, scale):
         for i in range(n):
             keys, vals = [], []
             b = 0
-            while b * pool + pool - 1 <= i - window:
+            while pool and b * pool + pool - 1 <= i - window:
                 keys.append(k[b * pool:(b + 1) * pool, g].mean(0))
                 vals.append(v[b * pool:(b + 1) * pool, g].mean(0))
                 b += 1

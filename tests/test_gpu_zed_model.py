@@ -1,0 +1,163 @@
+"""The Zedotar family on the GPU against the plain oracle (oracle/zedotar.py): whole prompts and every layer's stream,
+the first tokens, decoding token by token through the cache, prompts cut into portions, ragged batches, reused slots,
+long decoding with a growing cache, other sizes, both dtypes, greedy generation through the engine and its queue."""
+import pytest
+import torch
+
+import zed_helpers as H
+from oracle import zedotar as O
+
+pytestmark = pytest.mark.gpu
+TOL32 = 3e-5          # fp32 product vs float64 oracle: per-row rms of the logit difference over the logits' rms
+
+
+def toks(n, vocab, seed):
+    return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+@pytest.fixture(scope="module")
+def mixed():
+    t = H.random_tensors(H.MIXED, seed=1)
+    return H.MIXED, H.oracle_model(H.MIXED, t), H.product_model(H.MIXED, t, torch.float32)
+
+
+def run(model, pieces):
+    """Feed one sequence as the given portions through a fresh slot; -> logits of every position."""
+    slot = model.cache.alloc_slot()
+    out = [model.forward([(slot, p, range(len(p)))]) for p in pieces]
+    model.cache.free_slot(slot)
+    return torch.cat(out)
+
+
+def cut(seq, sizes):
+    out, i = [], 0
+    for s in sizes:
+        out.append(seq[i:i + s])
+        i += s
+    if i < len(seq):
+        out.append(seq[i:])
+    return [p for p in out if p]
+
+
+def test_whole_prompt_and_layers(mixed):
+    cfg, om, pm = mixed
+    seq = toks(70, cfg["vocab"], 2)
+    ref, streams = O.forward(om, seq, layer_out=True)
+    slot = pm.cache.alloc_slot()
+    got, ly = pm.forward([(slot, seq, range(len(seq)))], layer_out=True)
+    pm.cache.free_slot(slot)
+    for i in range(len(cfg["layers"])):
+        assert H.row_err(ly[i], streams[i]) < TOL32, f"layer {i}"
+    assert H.row_err(got, ref) < TOL32
+
+
+def test_first_tokens(mixed):
+    cfg, om, pm = mixed
+    for n in (1, 2, 3):
+        seq = toks(n, cfg["vocab"], 10 + n)
+        assert H.row_err(run(pm, [seq]), O.forward(om, seq)) < TOL32
+
+
+def test_prefill_then_token_by_token(mixed):
+    """Decoding walks windows over decoded tokens, completes pooled blocks one token at a time and carries the
+    convolution's rows and the matrix memory from step to step."""
+    cfg, om, pm = mixed
+    seq = toks(75, cfg["vocab"], 3)
+    ref = O.forward(om, seq)
+    for first in (1, 6, 30):
+        got = run(pm, [seq[:first]] + [[t] for t in seq[first:]])
+        assert H.row_err(got, ref) < TOL32, first
+
+
+def test_portions_down_to_two_tokens(mixed):
+    cfg, om, pm = mixed
+    seq = toks(90, cfg["vocab"], 4)
+    ref = O.forward(om, seq)
+    for sizes in ([2, 2, 2, 3, 1, 2, 17, 4, 31], [64, 2], [3] * 30, [5, 64], [1, 2, 70]):
+        assert H.row_err(run(pm, cut(seq, sizes)), ref) < TOL32, sizes
+
+
+def test_unequal_batch_equals_each_alone(mixed):
+    cfg, om, pm = mixed
+    seqs = [toks(n, cfg["vocab"], 20 + n) for n in (1, 37, 66, 9)]
+    refs = [O.forward(om, s + toks(12, cfg["vocab"], 50 + len(s))) for s in seqs]
+    tails = [toks(12, cfg["vocab"], 50 + len(s)) for s in seqs]
+    slots = [pm.cache.alloc_slot() for _ in seqs]
+    got = pm.forward([(slots[i], s, range(len(s))) for i, s in enumerate(seqs)])
+    o = 0
+    for s, r in zip(seqs, refs):
+        assert H.row_err(got[o:o + len(s)], r[:len(s)]) < TOL32
+        o += len(s)
+    live = list(range(len(seqs)))
+    for step in range(12):                             # decode together; one request leaves every fourth step
+        if step in (4, 8):
+            pm.cache.free_slot(slots[live.pop(1)])
+        got = pm.forward([(slots[i], [tails[i][step]], [0]) for i in live])
+        for k, i in enumerate(live):
+            assert H.row_err(got[k:k + 1], refs[i][len(seqs[i]) + step][None]) < TOL32, (step, i)
+    for i in live:
+        pm.cache.free_slot(slots[i])
+
+
+def test_freed_slots_are_used_again(mixed):
+    """Nothing is cleared on free: the next owner of a slot must not see its predecessor's keys, blocks, rows or memory."""
+    cfg, om, pm = mixed
+    a, b = toks(80, cfg["vocab"], 5), toks(23, cfg["vocab"], 6)
+    s = pm.cache.alloc_slot()
+    pm.forward([(s, a, [])])
+    pm.cache.free_slot(s)
+    s2 = pm.cache.alloc_slot()
+    assert s2 == s or pm.cache.live_slots == 1
+    got = torch.cat([pm.forward([(s2, b[:7], range(7))])] + [pm.forward([(s2, [t], [0])]) for t in b[7:]])
+    pm.cache.free_slot(s2)
+    assert H.row_err(got, O.forward(om, b)) < TOL32
+
+
+def test_long_decoding_with_a_growing_cache():
+    cfg = dict(H.MIXED, layers=H.MIXED["layers"][:3])
+    t = H.random_tensors(cfg, seed=7)
+    om, pm = H.oracle_model(cfg, t), H.product_model(cfg, t, torch.float32, max_tokens=16)
+    assert pm.cache.capacity == 16
+    seq = toks(150, cfg["vocab"], 8)
+    got = run(pm, [seq[:10]] + [[t] for t in seq[10:]])
+    assert pm.cache.capacity >= 150                    # the windowless cache and the block table grew, keeping their rows
+    assert H.row_err(got, O.forward(om, seq)) < TOL32
+
+
+def test_other_sizes_and_bf16():
+    t = H.random_tensors(H.ALIGNED, seed=3)
+    om = H.oracle_model(H.ALIGNED, t)
+    seq = toks(100, H.ALIGNED["vocab"], 9)
+    ref = O.forward(om, seq)
+    pm = H.product_model(H.ALIGNED, t, torch.float32)
+    assert H.row_err(run(pm, [seq]), ref) < TOL32
+    assert H.row_err(run(pm, cut(seq, [40, 2, 1, 1, 30])), ref) < TOL32
+    pb = H.product_model(H.ALIGNED, t, torch.bfloat16)
+    whole, parts = run(pb, [seq]), run(pb, [seq[:70]] + [[x] for x in seq[70:]])
+    # bf16 operands: a row whose mLSTM read-out nearly cancels amplifies the rounding, so the bound is on the typical row
+    # and on how many rows stray, not on the worst one
+    for a, b in ((whole, ref), (parts, ref), (parts, whole)):      # ... and the same numbers however the prompt was cut
+        rows = H.row_errs(a, b)
+        assert float(rows.median()) < 0.05 and float((rows > 0.15).double().mean()) < 0.1
+
+
+def test_greedy_generation_through_engine_and_queue(mixed):
+    from umbrella_b200.speculation.auto_engine import AutoEngine
+    cfg, om, pm = mixed
+    eng = AutoEngine.from_config("cuda:0", engine="batch", model=pm.model_name, dtype="float32", max_batch=2, temperature=0.0)
+    eng.initialize()                                   # registry -> config reader -> checkpoint loader
+    prompts = [toks(n, cfg["vocab"], 70 + n) for n in (5, 21, 2)]
+    outs = eng.generate_batch(prompts, max_new_tokens=6)          # three requests, two slots: two batches
+    assert eng.model.cache.live_slots == 0
+    assert eng.generate(input_ids=prompts[1], max_new_tokens=6)["generated_tokens"] == outs[1]
+    for p, out in zip(prompts, outs):
+        seq = list(p)
+        for tok in out:
+            logits = O.forward(om, seq)[-1]
+            best = int(logits.argmax())
+            if best != tok:                            # only a near tie may differ
+                assert float(logits[best] - logits[tok]) < 1e-3
+            seq.append(tok)
+    eng.update_generation_args(temperature=0.8, topk=8, topp=0.9)
+    sampled = eng.generate_batch(prompts[:2], max_new_tokens=5)
+    assert all(len(x) == 5 and all(0 <= y < cfg["vocab"] for y in x) for x in sampled)

@@ -109,3 +109,70 @@ def test_seq_abi_table_matches_header_and_library():
         assert hasattr(lib, n), n
     lib.umbs_version.restype = ctypes.c_char_p
     assert lib.umbs_version().startswith(b"umbrella_b200_seq")
+
+
+# ---------------------------------------------------------------------------------------------- the Zedotar family
+def test_zedotar_config_reader_and_tensor_names():
+    import zed_helpers as Z
+    from umbrella_b200.models.zedotar import layer_tensor_names, spec_from_config
+    spec = spec_from_config(Z.config_json(Z.MIXED))
+    assert (spec.width, spec.vocab, spec.norm_eps, spec.norm_offset, spec.logit_softcap) == (64, 96, 1e-5, 1.0, 12.0)
+    ml, at, a2 = spec.layers[0], spec.layers[1], spec.layers[2]
+    assert all(l.form == "prenorm" and not l.shift and not l.depth_average and l.norm_offset == 1.0 for l in spec.layers)
+    assert (ml.mixer, ml.heads, ml.dim, ml.vdim, ml.gate_cap, ml.mlp.shared_ff, ml.mlp.act) == ("mlstm", 3, 16, 20, 10.0, 48, "gelu_tanh")
+    assert (at.mixer, at.attn_mode, at.gate_kind, at.kv_heads, at.window, at.pool, at.taps, at.values_are_keys, at.bias, at.head_bias) == \
+        ("cached_attention", "softmax_sink", 1, 2, 9, 4, 1, False, True, False)
+    assert (a2.mixer, a2.attn_mode, a2.gate_kind, a2.window, a2.pool, a2.taps, a2.values_are_keys, a2.head_bias, a2.mlp) == \
+        ("cached_attention", "sigmoid", 2, 0, 0, 3, True, True, None)
+    assert spec.layers[3].rot_dims == 0 and spec.layers[3].inv_freq is None and spec.layers[5].taps == 1
+    assert spec_from_config(Z.config_json(Z.ALIGNED)).logit_softcap == 0.0
+    names = {n for i in range(len(spec.layers)) for v in layer_tensor_names(spec, i).values() for n in ([v] if isinstance(v, str) else v)}
+    assert names | {"embed", "head", "final.norm"} == set(Z.random_tensors(Z.MIXED))
+    bad = Z.config_json(Z.MIXED)
+    bad["layers"][2]["mixer"]["vdim"] = 24                            # values are the keys: vdim must equal dim
+    with pytest.raises(ValueError):
+        spec_from_config(bad)
+    with pytest.raises(ValueError):
+        spec_from_config(dict(Z.config_json(Z.MIXED), architecture="Radanex"))
+
+
+def test_zedotar_rotary_frequencies_match_the_plain_statement():
+    import zed_helpers as Z
+    from oracle import zedotar as O
+    from umbrella_b200.models.zedotar import spec_from_config
+    cfg = dict(Z.MIXED, layers=[dict(Z.ATT, ff=None), dict(Z.AT2, ff=None),
+                                dict(Z.ATT, rot=dict(dims=16, base=500.0, scaling=dict(factor=8.0, low=0.5, high=2.0, original=12)), ff=None),
+                                dict(Z.AT2, rot=dict(dims=16, base=40.0, scaling=dict(factor=4.0, original=64, fast=16.0, slow=2.0)), ff=None)])
+    spec = spec_from_config(Z.config_json(cfg))
+    for L, l in zip(cfg["layers"], spec.layers):
+        f, mag = O.rotary_frequencies(Z._rot(L))
+        assert torch.allclose(torch.tensor(l.inv_freq, dtype=torch.float64), f, rtol=1e-12, atol=0)
+        assert abs(l.rot_mag - mag) < 1e-12
+    f = [x for l in spec.layers for x in l.inv_freq]
+    assert len(set(f)) > len(f) // 2                                  # the rules leave distinct frequencies (no collapse)
+
+
+def test_state_cache_of_cached_attention_and_mlstm_layers():
+    import zed_helpers as Z
+    from umbrella_b200.attn.state_cache import SequenceStateCache
+    from umbrella_b200.models.zedotar import spec_from_config
+    spec = spec_from_config(Z.config_json(Z.MIXED))
+    c = SequenceStateCache(spec, slots=2, device="cpu", dtype=torch.float32, capacity=24)
+    assert c.capacity == 24 and c.mlstm_state[0].shape == (2, 3, 16 * 21 + 1) and c.shift[0] is None
+    assert c.kv_cache[1].shape == (2, 9, 2 * 40) and c.pool_cache[1].shape == (2, 6, 80)          # ring of the window; 24 / 4 blocks
+    assert c.kv_cache[2].shape == (2, 24, 2 * 32) and c.conv_state[2].shape == (2, 2, 2, 96) and c.pool_cache[2] is None
+    assert c.kv_cache[6].shape == (2, 7, 40)                                                       # blocks larger than the window
+    c.kv_cache[2][1, 23].fill_(4.0), c.pool_cache[1][1, 5].fill_(2.0), c.mlstm_state[0][1].fill_(1.5)
+    v = c.version
+    c.reserve_length(24)
+    assert c.version == v
+    c.reserve_length(25)                                              # the growing parts double and keep their rows
+    assert c.capacity == 48 and c.version > v
+    assert c.kv_cache[2].shape == (2, 48, 64) and float(c.kv_cache[2][1, 23].min()) == 4.0 and float(c.kv_cache[2][1, 24:].abs().max()) == 0
+    assert c.pool_cache[1].shape == (2, 12, 80) and float(c.pool_cache[1][1, 5].min()) == 2.0
+    assert c.kv_cache[1].shape == (2, 9, 80) and float(c.mlstm_state[0][1].min()) == 1.5
+    s = [c.alloc_slot() for _ in range(3)]                            # more slots: every part keeps what it holds
+    assert c.slots == 4 and c.kv_cache[2].shape == (4, 48, 64) and float(c.kv_cache[2][1, 23].min()) == 4.0
+    capped = SequenceStateCache(spec, slots=1, device="cpu", dtype=torch.float32, max_length=30)
+    with pytest.raises(RuntimeError):
+        capped.reserve_length(31)

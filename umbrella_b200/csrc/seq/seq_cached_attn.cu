@@ -230,6 +230,147 @@ static int launch_any(int mode, const CachedAttnArgs& a, const Batch& b, cudaStr
     return UMB_ERR_ARG;
 }
 
+
+// ------------------------------------------------------------------------------------------------ decode steps
+// One block = (split, head, sequence) of a step with one token per sequence.  The row's keys -- pooled blocks first,
+// then the tokens of its window -- are numbered 0 .. n - 1 and cut into n_split equal runs; inside a block warp w takes
+// keys w, w + 8, ... of the run, lanes striding over the head's dimensions, with its own running (maximum, sum, output).
+// The warps' triples are merged in shared memory; one split writes the output itself, several leave their triples in
+// `part` [(token, head), split, vdim + 2] for cached_attention_merge_kernel.
+constexpr int kCdWarps = 8, kCdMaxPerLane = 4;        // dim, vdim <= 128
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(32 * kCdWarps) cached_attention_decode_kernel(CachedAttnArgs a, Batch b, int n_split,
+                                                                                float* __restrict__ part) {
+    __shared__ float sm_o[kCdWarps][128];
+    __shared__ float sm_ml[kCdWarps][2];
+    const int split = blockIdx.x, h = blockIdx.y, s = blockIdx.z;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int dim = a.dim, vdim = a.vdim;
+    const int t = b.seq_start[s], p = b.seq_pos0[s], slot = b.seq_slot[s];
+    const int g = h / (a.heads / a.kv_heads);
+    const int row_kv = a.kv_heads * (dim + vdim), koff = g * dim, voff = a.kv_heads * dim + g * vdim;
+    const int window = a.window > 0 ? a.window : (1 << 30);
+    const int n_pool = pooled_visible(p, window, a.pool), j_lo = max(0, p - window + 1);
+    const int n_keys = n_pool + (p - j_lo + 1);
+    const int per = (n_keys + n_split - 1) / n_split, lo = split * per, hi = min(n_keys, lo + per);
+    const T* qrow = (const T*)a.q + (int64_t)t * a.heads * dim + (int64_t)h * dim;
+    float qv[kCdMaxPerLane], o[kCdMaxPerLane];
+#pragma unroll
+    for (int i = 0; i < kCdMaxPerLane; ++i) {
+        const int d = lane + 32 * i;
+        qv[i] = d < dim ? to_f32(qrow[d]) : 0.f;
+        o[i] = 0.f;
+    }
+    const float hb = (MODE == UMBS_ATTN_SIGMOID && a.head_bias) ? a.head_bias[h] : 0.f;
+    float m = -INFINITY, l = 0.f;
+    for (int k = lo + w; k < hi; k += kCdWarps) {
+        const T* src;
+        if (k < n_pool) src = (const T*)a.pool_cache + ((int64_t)slot * a.pool_len + k) * row_kv;
+        else {
+            const int j = j_lo + (k - n_pool);
+            src = j >= p ? (const T*)a.kv + (int64_t)t * row_kv : (const T*)a.kv_cache + ((int64_t)slot * a.kv_len + j % a.kv_len) * row_kv;
+        }
+        float dot = 0.f, vv[kCdMaxPerLane];
+#pragma unroll
+        for (int i = 0; i < kCdMaxPerLane; ++i) {
+            const int d = lane + 32 * i;
+            if (d < dim) dot = fmaf(qv[i], to_f32(src[koff + d]), dot);
+            vv[i] = d < vdim ? to_f32(src[voff + d]) : 0.f;
+        }
+#pragma unroll
+        for (int x = 16; x > 0; x >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, x);
+        float pw;
+        if (MODE == UMBS_ATTN_SIGMOID) {
+            pw = sigmoidf_(dot * a.scale + hb);
+        } else {
+            const float sc = dot * a.scale, mn = fmaxf(m, sc), corr = expf(m - mn);      // m = -inf the first time: corr = 0
+            pw = expf(sc - mn);
+            l = l * corr + pw;
+            m = mn;
+#pragma unroll
+            for (int i = 0; i < kCdMaxPerLane; ++i) o[i] *= corr;
+        }
+#pragma unroll
+        for (int i = 0; i < kCdMaxPerLane; ++i) o[i] = fmaf(pw, vv[i], o[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < kCdMaxPerLane; ++i) sm_o[w][lane + 32 * i] = o[i];
+    if (lane == 0) { sm_ml[w][0] = m; sm_ml[w][1] = l; }
+    __syncthreads();
+    // merge the warps' triples (in warp order); thread c < vdim owns output column c
+    const int c = threadIdx.x;
+    float M = -INFINITY, L = 0.f, O = 0.f;
+    if (MODE == UMBS_ATTN_SIGMOID) {
+        if (c < vdim)
+            for (int ww = 0; ww < kCdWarps; ++ww) O += sm_o[ww][c];
+    } else {
+        for (int ww = 0; ww < kCdWarps; ++ww) M = fmaxf(M, sm_ml[ww][0]);
+        if (n_split == 1 && MODE == UMBS_ATTN_SOFTMAX_SINK) M = fmaxf(M, 0.f);
+        for (int ww = 0; ww < kCdWarps; ++ww) {
+            const float mw = sm_ml[ww][0], f = mw > -INFINITY ? expf(mw - M) : 0.f;
+            L = fmaf(sm_ml[ww][1], f, L);
+            if (c < vdim) O = fmaf(sm_o[ww][c], f, O);
+        }
+        if (n_split == 1 && MODE == UMBS_ATTN_SOFTMAX_SINK) L += expf(-M);
+    }
+    if (n_split > 1) {
+        float* pr = part + (((int64_t)t * a.heads + h) * n_split + split) * (vdim + 2);
+        if (c < vdim) pr[c] = O;
+        if (c == 0) { pr[vdim] = M; pr[vdim + 1] = L; }
+        return;
+    }
+    if (c < vdim) {
+        const float inv = MODE == UMBS_ATTN_SIGMOID ? 1.f : 1.f / L;
+        float gt = 1.f;
+        if (a.gate) gt = sigmoidf_(a.gate[(int64_t)t * a.ldg + (a.gate_per_head ? h : h * vdim + c)]);
+        ((T*)a.out)[(int64_t)t * a.heads * vdim + (int64_t)h * vdim + c] = from_f32<T>(O * inv * gt);
+    }
+}
+
+// One block per (token, head): the splits' triples, in split order, then the sink, the division and the output gate.
+template <typename T, int MODE>
+__global__ void cached_attention_merge_kernel(CachedAttnArgs a, int n_split, const float* __restrict__ part) {
+    const int th = blockIdx.x, t = th / a.heads, h = th - t * a.heads, vdim = a.vdim, c = threadIdx.x;
+    const float* pr = part + (int64_t)th * n_split * (vdim + 2);
+    float M = MODE == UMBS_ATTN_SOFTMAX_SINK ? 0.f : -INFINITY, L = 0.f, O = 0.f;
+    if (MODE == UMBS_ATTN_SIGMOID) {
+        if (c < vdim)
+            for (int i = 0; i < n_split; ++i) O += pr[i * (vdim + 2) + c];
+    } else {
+        for (int i = 0; i < n_split; ++i) M = fmaxf(M, pr[i * (vdim + 2) + vdim]);
+        for (int i = 0; i < n_split; ++i) {
+            const float mi = pr[i * (vdim + 2) + vdim], f = mi > -INFINITY ? expf(mi - M) : 0.f;
+            L = fmaf(pr[i * (vdim + 2) + vdim + 1], f, L);
+            if (c < vdim) O = fmaf(pr[i * (vdim + 2) + c], f, O);
+        }
+        if (MODE == UMBS_ATTN_SOFTMAX_SINK) L += expf(-M);
+    }
+    if (c < vdim) {
+        const float inv = MODE == UMBS_ATTN_SIGMOID ? 1.f : 1.f / L;
+        float gt = 1.f;
+        if (a.gate) gt = sigmoidf_(a.gate[(int64_t)t * a.ldg + (a.gate_per_head ? h : h * vdim + c)]);
+        ((T*)a.out)[(int64_t)t * a.heads * vdim + (int64_t)h * vdim + c] = from_f32<T>(O * inv * gt);
+    }
+}
+
+template <typename T, int MODE>
+static int launch_decode(const CachedAttnArgs& a, const Batch& b, int n_split, float* part, cudaStream_t st) {
+    cached_attention_decode_kernel<T, MODE><<<dim3(n_split, a.heads, b.n_seqs), 32 * kCdWarps, 0, st>>>(a, b, n_split, part);
+    if (n_split > 1) cached_attention_merge_kernel<T, MODE><<<b.n_tokens * a.heads, 128, 0, st>>>(a, n_split, part);
+    return 0;
+}
+
+template <typename T>
+static int launch_decode_any(int mode, const CachedAttnArgs& a, const Batch& b, int n_split, float* part, cudaStream_t st) {
+    switch (mode) {
+        case UMBS_ATTN_SOFTMAX: return launch_decode<T, UMBS_ATTN_SOFTMAX>(a, b, n_split, part, st);
+        case UMBS_ATTN_SOFTMAX_SINK: return launch_decode<T, UMBS_ATTN_SOFTMAX_SINK>(a, b, n_split, part, st);
+        case UMBS_ATTN_SIGMOID: return launch_decode<T, UMBS_ATTN_SIGMOID>(a, b, n_split, part, st);
+    }
+    return UMB_ERR_ARG;
+}
+
 }  // namespace umbs
 
 using namespace umbs;
@@ -246,8 +387,27 @@ extern "C" int umbs_cached_attention(int dtype, int mode, const void* q, const v
     cudaStream_t st = (cudaStream_t)stream;
     CachedAttnArgs a{q, kv, kv_cache, pool_cache, kv_len, pool_len, heads, kv_heads, dim, vdim, window, pool, scale,
                      head_bias, gate, ldg, gate_per_head, out};
-    (void)split_scratch; (void)split_bytes;
     int rc;
+    if (batch->max_seq_len == 1) {
+        // a decode step: about 256 keys per block, as many splits as the longest context of the step asks for, the GPU
+        // has room for (two blocks per SM) and the scratch buffer holds
+        const int keys = window > 0 ? (batch->max_pos0 < window ? batch->max_pos0 + 1 : window + (pool > 0 ? batch->max_pos0 / pool : 0))
+                                    : batch->max_pos0 + 1;
+        int n_split = (keys + 255) / 256;
+        const int rows = batch->n_seqs * heads;
+        n_split = n_split < 1 ? 1 : (n_split > 32 ? 32 : n_split);
+        if (n_split > (296 + rows - 1) / rows) n_split = (296 + rows - 1) / rows;
+        const size_t per_split = (size_t)rows * (vdim + 2) * sizeof(float);
+        if (split_scratch == nullptr || per_split == 0) n_split = 1;
+        else if ((size_t)n_split * per_split > split_bytes) n_split = (int)(split_bytes / per_split);
+        if (n_split < 1) n_split = 1;
+        if (dtype == UMBS_BF16) rc = launch_decode_any<__nv_bfloat16>(mode, a, *batch, n_split, split_scratch, st);
+        else if (dtype == UMBS_F32) rc = launch_decode_any<float>(mode, a, *batch, n_split, split_scratch, st);
+        else return UMB_ERR_ARG;
+        if (rc) return rc;
+        count_launches(n_split > 1 ? 2 : 1);
+        return (int)cudaGetLastError();
+    }
     if (dtype == UMBS_BF16) rc = launch_any<__nv_bfloat16>(mode, a, *batch, st);
     else if (dtype == UMBS_F32) rc = launch_any<float>(mode, a, *batch, st);
     else return UMB_ERR_ARG;

@@ -158,3 +158,68 @@ def depth_mix(x, mix, stack, layer: int, depth_w, pair_out=None, sel_w=None, pai
     S.check(S.load().umbs_depth_mix(_p(x), _p(mix), _p(pair_out), _p(sel_w), _p(pair_pos), top, _p(shared), _p(stack), layer,
                                     _p(depth_w), _p(out), None, n, width, _stream()), "depth_mix")
     return out
+
+
+# ---------------------------------------------------------------------------------------------- pre-norm layers
+def add_rms_norm(x, delta, w, w_offset: float, eps: float, dtype=torch.float32, rows=None, want_copy: bool = False):
+    """x [n, width] fp32 (+= delta in place when ``rows`` is None) -> norm as ``dtype`` (and a copy of the sum)."""
+    n = x.shape[0] if rows is None else rows.numel()
+    y = torch.empty((n, x.shape[1]), dtype=dtype, device=x.device)
+    copy = torch.empty((n, x.shape[1]), dtype=torch.float32, device=x.device) if want_copy else None
+    S.check(S.load().umbs_add_rms_norm(_mode(y), _p(x), _p(delta), _p(rows), n, _p(w), float(w_offset), x.shape[1], float(eps),
+                                       _p(y), _p(copy), _stream()), "add_rms_norm")
+    return (y, copy) if want_copy else y
+
+
+def softcap(z: torch.Tensor, cap: float) -> torch.Tensor:
+    assert z.dtype == torch.float32 and z.is_contiguous()
+    S.check(S.load().umbs_softcap(_p(z), z.numel(), float(cap), _stream()), "softcap")
+    return z
+
+
+def attention_prep(proj, bias, batch: RaggedBatch, heads, kv_heads, dim, vdim, rot_dims, inv_freq, rot_mag=1.0,
+                   values_are_keys=False, taps=1, conv_w=None, conv_state=None, dtype=torch.float32):
+    """proj fp32 [T, q | k | v | ...] -> (q [T, heads dim], kv [T, kv_heads (dim + vdim)]) as ``dtype``."""
+    T = proj.shape[0]
+    q = torch.empty((T, heads * dim), dtype=dtype, device=proj.device)
+    kv = torch.empty((T, kv_heads * (dim + vdim)), dtype=dtype, device=proj.device)
+    slots = conv_state.shape[1] if conv_state is not None else 0
+    S.check(S.load().umbs_attention_prep(_mode(q), _p(proj), proj.stride(0), _p(bias), C.byref(batch.c), heads, kv_heads, dim,
+                                         vdim, int(values_are_keys), taps, _p(conv_w), _p(conv_state), slots, rot_dims,
+                                         _p(inv_freq), float(rot_mag), _p(q), _p(kv), _stream()), "attention_prep")
+    return q, kv
+
+
+def cached_attention(q, kv, kv_cache, batch: RaggedBatch, heads, kv_heads, dim, vdim, scale, mode=S.UMBS_ATTN_SOFTMAX,
+                     window=0, pool=0, pool_cache=None, head_bias=None, gate=None, gate_per_head=False, append=True,
+                     split=True):
+    """One attention step over the step's kv rows and the slots' caches (pooling the blocks the step completes first and
+    appending the step's rows afterwards, as umbs_forward does)."""
+    T = q.shape[0]
+    lib, row = S.load(), kv_heads * (dim + vdim)
+    out = torch.empty((T, heads * vdim), dtype=q.dtype, device=q.device)
+    if pool > 0:
+        S.check(lib.umbs_kv_pool(_mode(q), _p(kv), _p(kv_cache), kv_cache.shape[1], _p(pool_cache), pool_cache.shape[1],
+                                 C.byref(batch.c), row, pool, _stream()), "kv_pool")
+    part = torch.empty(2048 * (vdim + 2), dtype=torch.float32, device=q.device) if split else None
+    S.check(lib.umbs_cached_attention(_mode(q), mode, _p(q), _p(kv), _p(kv_cache), kv_cache.shape[1], _p(pool_cache),
+                                      pool_cache.shape[1] if pool_cache is not None else 0, C.byref(batch.c), heads, kv_heads,
+                                      dim, vdim, window, pool, float(scale), _p(head_bias), _p(gate),
+                                      gate.stride(0) if gate is not None else 0, int(gate_per_head), _p(part),
+                                      part.numel() * 4 if part is not None else 0, _p(out), _stream()), "cached_attention")
+    if append:
+        S.check(lib.umbs_ring_append(_mode(q), _p(kv), _p(kv_cache), kv_cache.shape[1], C.byref(batch.c), row, _stream()),
+                "ring_append")
+    return out
+
+
+def mlstm(proj, gate_bias, batch: RaggedBatch, heads, dim, vdim, gate_cap, eps, out_norm_w, state, dtype=torch.float32):
+    """proj fp32 [T, q | k | v | gate | i | f] -> [T, heads vdim] as ``dtype``; state fp32 [slots, heads, dim (vdim + 1) + 1]."""
+    T = proj.shape[0]
+    gates = torch.empty((T, heads, 3), dtype=torch.float32, device=proj.device)
+    o32 = torch.empty((T, heads, vdim + 1), dtype=torch.float32, device=proj.device)
+    out = torch.empty((T, heads * vdim), dtype=dtype, device=proj.device)
+    S.check(S.load().umbs_mlstm(_mode(out), _p(proj), proj.stride(0), _p(gate_bias), C.byref(batch.c), heads, dim, vdim,
+                                float(gate_cap), float(eps), _p(out_norm_w), _p(state), _p(gates), _p(o32), _p(out), _stream()),
+            "mlstm")
+    return out
