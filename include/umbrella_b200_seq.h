@@ -288,10 +288,12 @@ int umbs_cached_attention(int dtype, int mode, const void* q, const void* kv, co
  * o = S_t^T (q dim^-1/2) / (max(|n_t . q dim^-1/2|, e^(-m_t)) + 1e-6); then o / rms(o) per head (eps inside the root)
  * times out_norm_w times sigmoid(gate) -> out (`dtype` [n_tokens, heads vdim]).  state: fp32 [slots, heads,
  * dim (vdim + 1) + 1] (S with n as its last column, then m; read as zero at position 0).  gates_scratch: fp32
- * [n_tokens, heads, 3]; o_scratch: fp32 [n_tokens, heads, vdim + 1]. */
+ * [n_tokens, heads, 3]; o_scratch: fp32 [n_tokens, heads, vdim + 1].  seg_scratch (optional, fp32, seg_bytes): room for
+ * segment states; with it a step of few long sequences is cut into segments that run side by side in two passes (as many
+ * segments as fit: heads (dim (vdim + 1) + 1) floats per sequence and segment). */
 int umbs_mlstm(int dtype, const float* proj, int64_t ld, const float* gate_bias, const umbs_batch_t* batch, int heads,
                int dim, int vdim, float gate_cap, float eps, const float* out_norm_w, float* state, float* gates_scratch,
-               float* o_scratch, void* out, umbs_stream_t stream);
+               float* o_scratch, float* seg_scratch, size_t seg_bytes, void* out, umbs_stream_t stream);
 
 int umbs_embedding(int dtype, const int32_t* ids, const void* table, float* y, int n, int width, umbs_stream_t stream);
 

@@ -267,3 +267,37 @@ def test_mlstm_whole_portions_and_batches(H, D, V, cap):
         for s in lens:
             if got[s]:
                 assert err(torch.cat(got[s]), refs[s][:at[s]]) < 2e-5, (s, len(lengths))
+
+
+def test_mlstm_long_sequences_cut_into_segments():
+    """A step of few long sequences runs as segments side by side (two passes, chained states): a long prompt that starts
+    from a carried state, with a short neighbour and one whose last segment is a single token, against the single walk
+    of the oracle."""
+    from umbrella_b200 import ops_seq as K
+    H, D, V, cap = 2, 32, 40, 8.0
+    rows = 2 * H * D + 2 * H * V + 2 * H
+    lens = {0: 10 + 417, 1: 5, 2: 3 + 321}
+    proj = {s: rnd(n, rows, seed=40 + s) for s, n in lens.items()}
+    for s in proj:
+        proj[s][:, -2 * H:] *= 4.0
+    bias, norm_w = rnd(2 * H, seed=43), 1.0 + rnd(H * V, seed=44, scale=0.2)
+    refs = {s: mlstm_reference(proj[s], bias, H, D, V, cap, 1e-5, norm_w) for s in lens}
+    state = torch.full((3, H, D * (V + 1) + 1), -1.5, dtype=torch.float32, device=DEV)
+    plan = steps_of([[(0, 10), (2, 3)], [(0, 417), (1, 5), (2, 321)]])
+    at, got = {0: 0, 1: 0, 2: 0}, {0: [], 1: [], 2: []}
+    for desc in plan:
+        x = torch.cat([proj[s][at[s]:at[s] + n] for s, n, _, _ in desc])
+        out = K.mlstm(f32(x), f32(bias), K.RaggedBatch(desc, DEV), H, D, V, cap, 1e-5, f32(norm_w), state, segments=True)
+        o = 0
+        for s, n, _, _ in desc:
+            got[s].append(out[o:o + n])
+            at[s] += n
+            o += n
+    for s in lens:
+        assert err(torch.cat(got[s]), refs[s]) < 3e-5, s
+    # the state the segmented step left is the single walk's: one more token from it
+    extra = rnd(1, rows, seed=49)
+    full = torch.cat([proj[0], extra])
+    ref = mlstm_reference(full, bias, H, D, V, cap, 1e-5, norm_w)[-1:]
+    out = K.mlstm(f32(extra), f32(bias), K.RaggedBatch([(0, 1, lens[0], 0)], DEV), H, D, V, cap, 1e-5, f32(norm_w), state)
+    assert err(out, ref) < 3e-5

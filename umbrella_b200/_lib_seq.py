@@ -92,7 +92,7 @@ SIGNATURES = {
                                       c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int64, c_int, c_void_p,
                                       c_size_t, c_void_p, c_void_p]),
     "umbs_mlstm": (c_int, [c_int, c_void_p, c_int64, c_void_p, _BP, c_int, c_int, c_int, c_float, c_float, c_void_p,
-                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "umbs_embedding": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
 }
 

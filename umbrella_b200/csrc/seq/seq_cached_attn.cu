@@ -6,7 +6,9 @@
 //
 // Tile kernel (any step): one block = 64 consecutive query rows of one (sequence, head); 256 threads as 16 x 16, a thread
 // owns 4 rows x 4 keys of the score tile and 4 rows x VC value columns of the output; per tile of 64 keys the scores come
-// from transposed fp32 tiles in shared memory, the weights go back through shared memory for the value product.
+// from transposed fp32 tiles in shared memory, the weights go back through shared memory for the value product.  The key
+// tile holds 64 dimensions at a time (larger heads add their scores up over several passes), which keeps two blocks on an
+// SM for heads of 128.
 // Decode kernel (one token per sequence): one block = (sequence, head, split); a warp takes every 8th key of the block's
 // share, lanes striding over the head's dimensions; partial (max, sum, output) triples are merged per block and, with more
 // than one split, by a second kernel.
@@ -14,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
+#include <algorithm>
 #include <stdint.h>
 
 #include "seq_internal.h"
@@ -21,6 +24,7 @@
 namespace umbs {
 
 constexpr int kCaQ = 64, kCaK = 64, kCaS = 68;        // rows and keys per tile; row stride of the [d][row] tiles
+constexpr int kCaD = 64;                              // dimensions of a key tile held at a time
 
 struct CachedAttnArgs {
     const void* q; const void* kv; const void* kv_cache; const void* pool_cache;
@@ -45,8 +49,8 @@ __global__ void __launch_bounds__(256) cached_attention_kernel(CachedAttnArgs a,
     constexpr int VW = 16 * VC, VP = VW + 4;
     const int dim = a.dim, vdim = a.vdim;
     float* Qs = sm;                                   // [dim][kCaS]  Qs[d][row]
-    float* Ks = Qs + (size_t)dim * kCaS;              // [dim][kCaS]  Ks[d][key]
-    float* Vs = Ks + (size_t)dim * kCaS;              // [kCaK][VP]
+    float* Ks = Qs + (size_t)dim * kCaS;              // [min(dim, kCaD)][kCaS]  Ks[d][key], kCaD dimensions at a time
+    float* Vs = Ks + (size_t)min(dim, kCaD) * kCaS;   // [kCaK][VP]
     float* Ps = Vs + (size_t)kCaK * VP;               // [kCaK][kCaS] Ps[key][row]
     const int s = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * kCaQ;
     const int len = b.seq_len[s], start = b.seq_start[s], pos0 = b.seq_pos0[s], slot = b.seq_slot[s];
@@ -81,43 +85,46 @@ __global__ void __launch_bounds__(256) cached_attention_kernel(CachedAttnArgs a,
         const bool in_pool = tile < tiles_pool;
         const int base = in_pool ? tile * kCaK : j_lo + (tile - tiles_pool) * kCaK;
         const int hi = in_pool ? n_pool - 1 : p_hi;                        // last index of this kind any row sees
-        __syncthreads();                              // the previous tile is consumed (first time round: Qs is written)
-        for (int i = tid; i < kCaK * dim; i += 256) {
-            const int kk = i / dim, d = i - kk * dim, j = base + kk;
-            float val = 0.f;
-            if (j <= hi) {
-                const T* src = in_pool ? pooled + ((int64_t)slot * a.pool_len + j) * row_kv
-                             : (j >= pos0 ? kv + (int64_t)(start + j - pos0) * row_kv
-                                          : cache + ((int64_t)slot * a.kv_len + j % a.kv_len) * row_kv);
-                val = to_f32(src[koff + d]);
-            }
-            Ks[d * kCaS + kk] = val;
-        }
-        for (int i = tid; i < kCaK * VW; i += 256) {
-            const int kk = i / VW, c = i - kk * VW, j = base + kk;
-            float val = 0.f;
-            if (j <= hi && c < vdim) {
-                const T* src = in_pool ? pooled + ((int64_t)slot * a.pool_len + j) * row_kv
-                             : (j >= pos0 ? kv + (int64_t)(start + j - pos0) * row_kv
-                                          : cache + ((int64_t)slot * a.kv_len + j % a.kv_len) * row_kv);
-                val = to_f32(src[voff + c]);
-            }
-            Vs[kk * VP + c] = val;
-        }
-        __syncthreads();
         float sc[4][4];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) sc[i][jj] = 0.f;
-        for (int d = 0; d < dim; ++d) {
-            const float4 qv = *reinterpret_cast<const float4*>(Qs + d * kCaS + ty * 4);
-            const float4 kv4 = *reinterpret_cast<const float4*>(Ks + d * kCaS + tx * 4);
-            const float qa[4] = {qv.x, qv.y, qv.z, qv.w}, ka[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
+        for (int d0 = 0; d0 < dim; d0 += kCaD) {
+            const int dc = min(kCaD, dim - d0);
+            __syncthreads();                          // the previous pass or tile is consumed (first time round: Qs is written)
+            for (int i = tid; i < kCaK * dc; i += 256) {
+                const int kk = i / dc, d = i - kk * dc, j = base + kk;
+                float val = 0.f;
+                if (j <= hi) {
+                    const T* src = in_pool ? pooled + ((int64_t)slot * a.pool_len + j) * row_kv
+                                 : (j >= pos0 ? kv + (int64_t)(start + j - pos0) * row_kv
+                                              : cache + ((int64_t)slot * a.kv_len + j % a.kv_len) * row_kv);
+                    val = to_f32(src[koff + d0 + d]);
+                }
+                Ks[d * kCaS + kk] = val;
+            }
+            for (int i = tid; d0 == 0 && i < kCaK * VW; i += 256) {
+                const int kk = i / VW, c = i - kk * VW, j = base + kk;
+                float val = 0.f;
+                if (j <= hi && c < vdim) {
+                    const T* src = in_pool ? pooled + ((int64_t)slot * a.pool_len + j) * row_kv
+                                 : (j >= pos0 ? kv + (int64_t)(start + j - pos0) * row_kv
+                                              : cache + ((int64_t)slot * a.kv_len + j % a.kv_len) * row_kv);
+                    val = to_f32(src[voff + c]);
+                }
+                Vs[kk * VP + c] = val;
+            }
+            __syncthreads();
+            for (int d = 0; d < dc; ++d) {
+                const float4 qv = *reinterpret_cast<const float4*>(Qs + (d0 + d) * kCaS + ty * 4);
+                const float4 kv4 = *reinterpret_cast<const float4*>(Ks + d * kCaS + tx * 4);
+                const float qa[4] = {qv.x, qv.y, qv.z, qv.w}, ka[4] = {kv4.x, kv4.y, kv4.z, kv4.w};
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+                for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) sc[i][jj] = fmaf(qa[i], ka[jj], sc[i][jj]);
+                    for (int jj = 0; jj < 4; ++jj) sc[i][jj] = fmaf(qa[i], ka[jj], sc[i][jj]);
+            }
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -202,7 +209,7 @@ __global__ void __launch_bounds__(256) cached_attention_kernel(CachedAttnArgs a,
 
 template <typename T, int VC, int MODE>
 static int launch_tiles(const CachedAttnArgs& a, const Batch& b, cudaStream_t st) {
-    const size_t smem = ((size_t)2 * a.dim * kCaS + (size_t)kCaK * (16 * VC + 4) + (size_t)kCaK * kCaS) * sizeof(float);
+    const size_t smem = ((size_t)(a.dim + std::min(a.dim, kCaD)) * kCaS + (size_t)kCaK * (16 * VC + 4) + (size_t)kCaK * kCaS) * sizeof(float);
     static size_t set = 0;
     if (smem > 48 * 1024 && smem > set) {
         cudaError_t e = cudaFuncSetAttribute(cached_attention_kernel<T, VC, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -75,6 +75,9 @@ static size_t carve(const umbs_model_t* m, int T, int n_want, char* base, Scratc
         } else if (l.mixer == UMBS_MIX_MLSTM) {
             up(in_rows, 2 * l.heads * l.dim + 2 * l.heads * l.vdim + 2 * l.heads);
             up(hv, l.heads * (l.vdim + 1));                        // o32 holds n . q as one more column per head
+            // segment states (and decay products) of a step of few long sequences: about 592 blocks' worth
+            const size_t plane = (size_t)l.heads * ((size_t)l.dim * (l.vdim + 1) + 1) * 4, ent = 592 / ((size_t)l.heads * ((l.vdim + 32) / 32)) + 8;
+            if (T >= 128 && ent * plane > segb) segb = ent * plane;
         } else if (l.mixer == UMBS_MIX_RETENTION) {
             up(in_rows, 2 * l.heads * l.dim + 2 * l.heads * l.vdim); up(rotd, l.rot_dims);
             // segment states of a step of few long sequences: about 592 blocks' worth (umbs_retention uses what fits)
@@ -183,7 +186,7 @@ extern "C" int umbs_forward(const umbs_model_t* m, const umbs_batch_t* b, float*
             const int rows = 2 * l.heads * l.dim + 2 * hv + 2 * l.heads;
             UMBS_TRY(umbs_gemm(dt, s.h, W, 0, l.w_in, W, 0, s.proj, rows, 0, 1, T, rows, W, 1, nullptr, nullptr, 0, 0.f, stream));
             UMBS_TRY(umbs_mlstm(dt, s.proj, rows, l.bias_in, b, l.heads, l.dim, l.vdim, l.gate_cap, m->norm_eps, l.out_norm_w,
-                                l.mlstm_state, s.gates, s.o32, s.mixed, stream));
+                                l.mlstm_state, s.gates, s.o32, s.seg_bytes ? s.seg : nullptr, s.seg_bytes, s.mixed, stream));
         } else {
             return UMB_ERR_UNSUPPORTED;
         }

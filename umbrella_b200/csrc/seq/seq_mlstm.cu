@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
+#include <algorithm>
 #include <stdint.h>
 
 #include "seq_internal.h"
@@ -65,10 +66,17 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ proj, int64_t ld, i
 }
 
 // See retention_kernel (seq_kernels.cu) for the walk; here V1 = vdim + 1 columns (the last one is n), per-token factors.
+// A sequence may be cut into n_seg segments of seg_len tokens that run as blocks of their own (blockIdx.x = sequence *
+// n_seg + segment), in two passes, as retention does: pass 1 runs every segment but a sequence's last from a zero state
+// and leaves its end state L_g in seg_state and the product A_g of its tokens' decays in seg_decay; mlstm_chain_kernel
+// turns these into start states (S_(g+1) = A_g S_g + L_g); pass 2 starts every segment from its entry and writes the
+// outputs, and the last segment stores the slot's state.  pass 0: no segments.  The gates (and with them the running
+// maximum every factor refers to) come from the gates kernel, which always walks whole sequences.
 template <int DPT, int TB>
 __global__ void mlstm_kernel(const float* __restrict__ proj, int64_t ld, Batch b, int heads, int dim, int vdim,
                              const float* __restrict__ gates, float* __restrict__ state, int64_t state_stride,
-                             float* __restrict__ o_out) {
+                             float* __restrict__ o_out, int seg_len, int n_seg, int pass, float* __restrict__ seg_state,
+                             float* __restrict__ seg_decay) {
     extern __shared__ __align__(16) float sm[];
     const int DS = blockDim.y, dimP = DS * DPT, nthr = 32 * DS, V1 = vdim + 1;
     float* qs = sm;                          // [TB][dimP]
@@ -76,15 +84,31 @@ __global__ void mlstm_kernel(const float* __restrict__ proj, int64_t ld, Batch b
     float* part = ks + TB * dimP;            // [DS][TB][32]
     float* vs = part + DS * TB * 32;         // [TB][32]
     float* as = vs + TB * 32;                // [TB]         the tokens' decays
-    const int s = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, w = threadIdx.y, tid = w * 32 + lane;
+    const int s = blockIdx.x / n_seg, seg = blockIdx.x - s * n_seg;
+    const int h = blockIdx.y, lane = threadIdx.x, w = threadIdx.y, tid = w * 32 + lane;
     const int j = blockIdx.z * 32 + lane, d0 = w * DPT;
-    const int len = b.seq_len[s], start = b.seq_start[s], pos0 = b.seq_pos0[s], slot = b.seq_slot[s];
+    const int seq_len = b.seq_len[s], t_first = seg * seg_len;
+    if (t_first >= seq_len) return;
+    const int len = min(seg_len, seq_len - t_first), start = b.seq_start[s] + t_first;
+    const bool last_seg = t_first + len == seq_len;
+    if (pass == 1 && last_seg) return;
+    const int pos0 = b.seq_pos0[s], slot = b.seq_slot[s];
     const bool col = j < V1;
     const float qscale = 1.f / sqrtf((float)dim);
+    const int64_t plane = (int64_t)heads * dim * V1;
     float* st = state + ((int64_t)slot * heads + h) * state_stride;
-    float S[DPT];
+    const float* st_in = st;
+    bool have = pos0 > 0;
+    if (pass == 1) have = false;
+    else if (pass == 2 && !(seg == 0 && last_seg)) {
+        // segment 0 of a cut sequence reads the chain kernel's copy of the slot's state (entry n_seg - 1), not the slot,
+        // which the sequence's last segment overwrites during this very launch
+        st_in = seg_state + ((int64_t)s * n_seg + (seg > 0 ? seg - 1 : n_seg - 1)) * plane + (int64_t)h * dim * V1;
+        have = true;
+    }
+    float S[DPT], decay_product = 1.f;
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) S[i] = (col && pos0 > 0 && d0 + i < dim) ? st[(int64_t)(d0 + i) * V1 + j] : 0.f;
+    for (int i = 0; i < DPT; ++i) S[i] = (col && have && d0 + i < dim) ? st_in[(int64_t)(d0 + i) * V1 + j] : 0.f;
     const int qoff = h * dim, koff = heads * dim + h * dim, voff = 2 * heads * dim + h * vdim;
     constexpr int EPT = TB * DPT / 32;
     float pq[EPT], pk[EPT], pv[TB], pa = 1.f;
@@ -131,6 +155,7 @@ __global__ void mlstm_kernel(const float* __restrict__ proj, int64_t ld, Batch b
         if (t0 + TB < len) fetch(t0 + TB);
         for (int tt = 0; tt < nb; ++tt) {
             const float v = vs[tt * 32 + lane], dec = as[tt];
+            decay_product *= dec;
             const float4* k4 = reinterpret_cast<const float4*>(ks + tt * dimP + d0);
             const float4* q4 = reinterpret_cast<const float4*>(qs + tt * dimP + d0);
             float acc = 0.f;
@@ -145,7 +170,7 @@ __global__ void mlstm_kernel(const float* __restrict__ proj, int64_t ld, Batch b
             part[(w * TB + tt) * 32 + lane] = acc;
         }
         __syncthreads();
-        for (int i = tid; i < nb * 32; i += nthr) {
+        for (int i = tid; i < nb * 32 && pass != 1; i += nthr) {
             const int tt = i >> 5, l = i & 31, jj = blockIdx.z * 32 + l;
             if (jj >= V1) continue;
             float o = 0.f;
@@ -153,10 +178,38 @@ __global__ void mlstm_kernel(const float* __restrict__ proj, int64_t ld, Batch b
             o_out[((int64_t)(start + t0 + tt) * heads + h) * V1 + jj] = o;
         }
     }
+    float* st_out = st;
+    if (pass == 1) {
+        st_out = seg_state + ((int64_t)s * n_seg + seg) * plane + (int64_t)h * dim * V1;
+        if (tid == 0 && blockIdx.z == 0) seg_decay[((int64_t)s * n_seg + seg) * heads + h] = decay_product;
+    } else if (pass == 2 && !last_seg) {
+        return;
+    }
     if (col) {
 #pragma unroll
         for (int i = 0; i < DPT; ++i)
-            if (d0 + i < dim) st[(int64_t)(d0 + i) * V1 + j] = S[i];
+            if (d0 + i < dim) st_out[(int64_t)(d0 + i) * V1 + j] = S[i];
+    }
+}
+
+// Between the two passes: one thread per state element walks the sequence's segments in order, S <- A_g S + L_g, and
+// overwrites L_g with the state segment g + 1 starts from; entry n_seg - 1 (never an end state) takes segment 0's start.
+__global__ void mlstm_chain_kernel(Batch b, int heads, int dim, int V1, const float* __restrict__ state, int64_t state_stride,
+                                   int seg_len, int n_seg, float* __restrict__ seg_state, const float* __restrict__ seg_decay) {
+    const int64_t plane = (int64_t)heads * dim * V1;
+    const int s = blockIdx.y;
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= plane) return;
+    const int full = (b.seq_len[s] - 1) / seg_len;          // segments that are followed by another one
+    if (full <= 0) return;
+    const int h = (int)(e / ((int64_t)dim * V1));
+    const int64_t in_head = e - (int64_t)h * dim * V1;
+    float S = b.seq_pos0[s] > 0 ? state[((int64_t)b.seq_slot[s] * heads + h) * state_stride + in_head] : 0.f;
+    float* p = seg_state + (int64_t)s * n_seg * plane + e;
+    p[(int64_t)(n_seg - 1) * plane] = S;
+    for (int g = 0; g < full; ++g) {
+        S = fmaf(seg_decay[((int64_t)s * n_seg + g) * heads + h], S, p[(int64_t)g * plane]);
+        p[(int64_t)g * plane] = S;
     }
 }
 
@@ -185,9 +238,10 @@ __global__ void mlstm_finish_kernel(const float* __restrict__ o, const float* __
 
 template <int DPT, int TB>
 static int launch_mlstm(const float* proj, int64_t ld, const Batch& b, int heads, int dim, int vdim, const float* gates,
-                        float* state, int64_t stride, float* o, cudaStream_t st) {
+                        float* state, int64_t stride, float* o, int seg_len, int n_seg, int pass, float* seg_state,
+                        float* seg_decay, cudaStream_t st) {
     const int ds = (dim + DPT - 1) / DPT;
-    const dim3 grid(b.n_seqs, heads, (vdim + 1 + 31) / 32), block(32, ds);
+    const dim3 grid(b.n_seqs * n_seg, heads, (vdim + 1 + 31) / 32), block(32, ds);
     const size_t smem = ((size_t)2 * TB * ds * DPT + (size_t)ds * TB * 32 + TB * 32 + TB) * sizeof(float);
     static size_t set = 0;
     if (smem > 48 * 1024 && smem > set) {
@@ -195,7 +249,8 @@ static int launch_mlstm(const float* proj, int64_t ld, const Batch& b, int heads
         if (e != cudaSuccess) return (int)e;
         set = smem;
     }
-    mlstm_kernel<DPT, TB><<<grid, block, smem, st>>>(proj, ld, b, heads, dim, vdim, gates, state, stride, o);
+    mlstm_kernel<DPT, TB><<<grid, block, smem, st>>>(proj, ld, b, heads, dim, vdim, gates, state, stride, o, seg_len, n_seg, pass,
+                                                     seg_state, seg_decay);
     return 0;
 }
 
@@ -205,7 +260,8 @@ using namespace umbs;
 
 extern "C" int umbs_mlstm(int dtype, const float* proj, int64_t ld, const float* gate_bias, const umbs_batch_t* batch,
                           int heads, int dim, int vdim, float gate_cap, float eps, const float* out_norm_w, float* state,
-                          float* gates_scratch, float* o_scratch, void* out, umbs_stream_t stream) {
+                          float* gates_scratch, float* o_scratch, float* seg_scratch, size_t seg_bytes, void* out,
+                          umbs_stream_t stream) {
     if (batch->n_tokens <= 0) return 0;
     if (heads < 1 || dim < 1 || vdim < 1 || !(gate_cap > 0.f) || out_norm_w == nullptr) return UMB_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
@@ -214,11 +270,40 @@ extern "C" int umbs_mlstm(int dtype, const float* proj, int64_t ld, const float*
     const int warps = batch->n_seqs * heads;
     mlstm_gates_kernel<<<(warps + 3) / 4, 128, 0, st>>>(proj, ld, off_i, off_f, gate_bias, *batch, heads, gate_cap, state, stride,
                                                         dim * (vdim + 1), gates_scratch);
+    // Few blocks and long sequences (one long prompt): cut the sequences into segments that run side by side in two passes.
+    // Twice the arithmetic of the recurrence for n_seg times the blocks; differs from the single walk by fp32 rounding only.
+    const int V1 = vdim + 1;
+    int n_seg = 1, seg_len = batch->max_seq_len;
+    const int base_blocks = batch->n_seqs * heads * ((V1 + 31) / 32);
+    const size_t per_seg = (size_t)batch->n_seqs * heads * ((size_t)dim * V1 + 1) * sizeof(float);      // states + decay products
+    if (seg_scratch != nullptr && base_blocks <= 148 && batch->max_seq_len >= 128) {
+        int want = std::min((592 + base_blocks - 1) / base_blocks, batch->max_seq_len / 64);
+        want = (int)std::min<size_t>(want, seg_bytes / per_seg);
+        if (want >= 2) {
+            seg_len = ((batch->max_seq_len + want - 1) / want + 15) & ~15;
+            n_seg = (batch->max_seq_len + seg_len - 1) / seg_len;
+        }
+    }
+    float* seg_decay = n_seg > 1 ? seg_scratch + (size_t)batch->n_seqs * n_seg * heads * dim * V1 : nullptr;
+    auto run = [&](int pass) -> int {
+        if (dim <= 32) return launch_mlstm<8, 16>(proj, ld, *batch, heads, dim, vdim, gates_scratch, state, stride, o_scratch, seg_len, n_seg, pass, seg_scratch, seg_decay, st);
+        if (dim <= 128) return launch_mlstm<16, 16>(proj, ld, *batch, heads, dim, vdim, gates_scratch, state, stride, o_scratch, seg_len, n_seg, pass, seg_scratch, seg_decay, st);
+        if (dim <= 512) return launch_mlstm<32, 8>(proj, ld, *batch, heads, dim, vdim, gates_scratch, state, stride, o_scratch, seg_len, n_seg, pass, seg_scratch, seg_decay, st);
+        return UMB_ERR_UNSUPPORTED;
+    };
     int rc;
-    if (dim <= 32) rc = launch_mlstm<8, 16>(proj, ld, *batch, heads, dim, vdim, gates_scratch, state, stride, o_scratch, st);
-    else if (dim <= 128) rc = launch_mlstm<16, 16>(proj, ld, *batch, heads, dim, vdim, gates_scratch, state, stride, o_scratch, st);
-    else if (dim <= 512) rc = launch_mlstm<32, 8>(proj, ld, *batch, heads, dim, vdim, gates_scratch, state, stride, o_scratch, st);
-    else return UMB_ERR_UNSUPPORTED;
+    unsigned launches = 3;
+    if (n_seg > 1) {
+        rc = run(1);
+        if (rc) return rc;
+        const int64_t plane = (int64_t)heads * dim * V1;
+        mlstm_chain_kernel<<<dim3((unsigned)((plane + 255) / 256), batch->n_seqs), 256, 0, st>>>(*batch, heads, dim, V1, state, stride,
+                                                                                             seg_len, n_seg, seg_scratch, seg_decay);
+        launches += 2;
+        rc = run(2);
+    } else {
+        rc = run(0);
+    }
     if (rc) return rc;
     const int fw = batch->n_tokens * heads;
     if (dtype == UMBS_BF16)
@@ -228,6 +313,6 @@ extern "C" int umbs_mlstm(int dtype, const float* proj, int64_t ld, const float*
         mlstm_finish_kernel<float><<<(fw + 3) / 4, 128, 0, st>>>(o_scratch, gates_scratch, proj, ld, off_g, batch->n_tokens, heads,
                                                                 vdim, eps, out_norm_w, (float*)out);
     else return UMB_ERR_ARG;
-    count_launches(3);
+    count_launches(launches);
     return (int)cudaGetLastError();
 }

@@ -213,13 +213,16 @@ def cached_attention(q, kv, kv_cache, batch: RaggedBatch, heads, kv_heads, dim, 
     return out
 
 
-def mlstm(proj, gate_bias, batch: RaggedBatch, heads, dim, vdim, gate_cap, eps, out_norm_w, state, dtype=torch.float32):
-    """proj fp32 [T, q | k | v | gate | i | f] -> [T, heads vdim] as ``dtype``; state fp32 [slots, heads, dim (vdim + 1) + 1]."""
+def mlstm(proj, gate_bias, batch: RaggedBatch, heads, dim, vdim, gate_cap, eps, out_norm_w, state, dtype=torch.float32,
+          segments: bool = True):
+    """proj fp32 [T, q | k | v | gate | i | f] -> [T, heads vdim] as ``dtype``; state fp32 [slots, heads, dim (vdim + 1) + 1].
+    ``segments``: give the kernel room to cut few long sequences into segments that run side by side."""
     T = proj.shape[0]
+    seg = torch.empty(32 * heads * (dim * (vdim + 1) + 1), dtype=torch.float32, device=proj.device) if segments and T >= 128 else None
     gates = torch.empty((T, heads, 3), dtype=torch.float32, device=proj.device)
     o32 = torch.empty((T, heads, vdim + 1), dtype=torch.float32, device=proj.device)
     out = torch.empty((T, heads * vdim), dtype=dtype, device=proj.device)
     S.check(S.load().umbs_mlstm(_mode(out), _p(proj), proj.stride(0), _p(gate_bias), C.byref(batch.c), heads, dim, vdim,
-                                float(gate_cap), float(eps), _p(out_norm_w), _p(state), _p(gates), _p(o32), _p(out), _stream()),
-            "mlstm")
+                                float(gate_cap), float(eps), _p(out_norm_w), _p(state), _p(gates), _p(o32), _p(seg),
+                                seg.numel() * 4 if seg is not None else 0, _p(out), _stream()), "mlstm")
     return out

@@ -57,10 +57,38 @@ class Timer:
         return total / reps
 
 
+def zedotar_config(width: int, layers: int = 8) -> dict:
+    """A Zedotar config with the layer sizes of a model of this width: mLSTM layers with a windowed attention layer as
+    every fourth and a convolved sigmoid-attention layer as the last; dense feed-forward of the width Radanex activates."""
+    heads = width // 128
+    rot = dict(dims=64, base=5e5)
+    mls = dict(type="mlstm", mixer=dict(heads=heads, dim=64, vdim=128, gate_cap=15.0))
+    att = dict(type="attention", mixer=dict(heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, scale=128 ** -0.5,
+                                            mask=dict(size=1024, pool=64),
+                                            rot=dict(rot, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192))))
+    at2 = dict(type="attention_2", mixer=dict(heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, conv=4, scale=128 ** -0.5,
+                                              rot=dict(rot, scaling=dict(factor=4.0, original=4096, fast=32.0, slow=1.0))))
+    mlp = dict(kind="dense", ff=2 * width)
+    kinds = [at2 if i == layers - 1 else (att if i % 4 == 3 else mls) for i in range(layers)]
+    return dict(architecture="Zedotar", width=width, vocab=32768, norm=dict(eps=1e-6), logit_softcap=30.0,
+                layers=[dict(k, mlp=mlp) for k in kinds])
+
+
 def bench_radanex(width, layers, device, prompt, ctx, batches, timer):
     from .models.radanex import Radanex, spec_from_config
     spec = spec_from_config(radanex_config(width, layers))
     m = Radanex(spec, device=device, dtype=torch.bfloat16, slots=max(batches))
+    return bench_seq_model(m, spec, prompt, ctx, batches, timer)
+
+
+def bench_zedotar(width, layers, device, prompt, ctx, batches, timer):
+    from .models.zedotar import Zedotar, spec_from_config
+    spec = spec_from_config(zedotar_config(width, layers))
+    m = Zedotar(spec, device=device, dtype=torch.bfloat16, slots=max(batches), max_tokens=prompt + ctx)
+    return bench_seq_model(m, spec, prompt, ctx, batches, timer)
+
+
+def bench_seq_model(m, spec, prompt, ctx, batches, timer):
     m.alloc()
     m.load_synthetic(7)
     g = torch.Generator().manual_seed(0)
@@ -258,6 +286,152 @@ def run(args):
             "data": "synthetic", "vs_baseline": None, "gpu_launches": int(launches),
             "config": {"name": "radanex", "workload": "prefill 1 x 2048 and 4 x 2048 tokens; decode at batch 1 / 8 / 64 behind a "
                        "512-token context; Llama fp16 of the same width, depth and active feed-forward size beside it",
+                       "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": how},
+                       "l2": "whole-model runs stream more than L2 per step; kernel table flushes L2 between runs"},
+            "sizes": sizes, "kernels": table}
+    print(json.dumps(line))
+
+
+def kernel_table_zedotar(zm, rm, device, timer, T=4096):
+    """Device time of each Zedotar mechanism at prefill size (one sequence of T tokens) and at decode size (8 sequences behind
+    512 tokens), with its roofline fractions, and the like kernel of the Radanex path measured the same way in the same
+    run (``like`` names the pairing)."""
+    from . import _lib_seq as S, ops_seq as Q
+    hbm, tflops, how = _peaks()
+    sp, W = zm.spec, zm.spec.width
+    fp32_peak = 148 * 128 * 2 * 1.965e-3
+    rows = []
+
+    def add(name, ms, nbytes=0, flops=0, like=None, flops32=0):
+        r = dict(kernel=name, ms=round(ms, 4))
+        if flops32:
+            r["fp32_tflops"], r["frac_of_fp32_fma_peak"] = round(flops32 / ms / 1e9, 2), round(flops32 / ms / 1e9 / fp32_peak, 3)
+        if flops:
+            r["tflops"], r["frac_of_bf16_peak"] = round(flops / ms / 1e9, 1), round(flops / ms / 1e9 / tflops, 3)
+        if nbytes:
+            r["gb_s"], r["frac_of_hbm_peak"] = round(nbytes / ms / 1e6, 1), round(nbytes / ms / 1e6 / hbm, 3)
+        if like:
+            r["like"] = like
+        rows.append(r)
+    mls = next(l for l in sp.layers if l.mixer == "mlstm")
+    att = next(l for l in sp.layers if l.mixer == "cached_attention" and l.window > 0)
+    at2 = next(l for l in sp.layers if l.mixer == "cached_attention" and l.window == 0)
+    mw, aw, sw = (zm.weights[sp.layers.index(l)] for l in (mls, att, at2))
+    rsp = rm.spec
+    ret = next(l for l in rsp.layers if l.mixer == "retention")
+    lat = next(l for l in rsp.layers if l.mixer == "latent_attention")
+    rw = rm.weights[rsp.layers.index(ret)]
+    bf = dict(dtype=torch.bfloat16, device=device)
+    ctx = 512
+    zm.cache.reserve_length(T)                       # the windowless cache and the block table hold the whole prompt
+    for n, tag in ((T, f"prefill T={T}"), (8, "decode T=8")):
+        nseq = 1 if n == T else 8
+        per = n // nseq
+        pos0 = 0 if n == T else ctx
+        batch = Q.RaggedBatch([(s, per, pos0, 0) for s in range(nseq)], device)
+        x, d = torch.randn(n, W, device=device), torch.randn(n, W, device=device)
+        h = torch.randn(n, W, **bf)
+        # feed-forward products
+        gu = mw["s_gu"]
+        ms = timer(lambda: Q.gemm(h, gu, dual=S.UMBS_ACT_GELU_TANH))
+        add(f"gemm dense gate|up + gelu [{n} x {W}] x [{gu.shape[0]} x {W}] ({tag})", ms,
+            nbytes=gu.numel() * 2 + n * W * 2 + n * gu.shape[0], flops=2 * n * W * gu.shape[0], like="gemm shared gate|up")
+        rgu = rw["s_gu"]
+        ms = timer(lambda: Q.gemm(h, rgu, dual=True, limit=7.0))
+        add(f"radanex gemm shared gate|up + clamped glu [{n} x {W}] x [{rgu.shape[0]} x {W}] ({tag})", ms,
+            nbytes=rgu.numel() * 2 + n * W * 2 + n * rgu.shape[0], flops=2 * n * W * rgu.shape[0])
+        # residual + norm
+        ms = timer(lambda: Q.add_rms_norm(x, d, mw["norm"], 1.0, sp.norm_eps, torch.bfloat16))
+        add(f"residual add + rms norm ({tag})", ms, nbytes=n * W * (4 + 4 + 4 + 2), like="group norm + token shift")
+        st = rm.cache.shift[rsp.layers.index(ret)]
+        ms = timer(lambda: Q.group_norm_shift(x, rw["norm"], rw["shift"], st, batch, rsp.norm_groups, rsp.norm_eps, torch.bfloat16))
+        add(f"radanex group norm + token shift ({tag})", ms, nbytes=n * W * (4 + 2 + 2))
+        # mLSTM beside retention (equal heads, dim, vdim)
+        ld = 2 * mls.heads * (mls.dim + mls.vdim) + 2 * mls.heads
+        proj = torch.randn(n, ld, device=device)
+        state = zm.cache.mlstm_state[sp.layers.index(mls)]
+        ms = timer(lambda: Q.mlstm(proj, mw["bias_in"], batch, mls.heads, mls.dim, mls.vdim, mls.gate_cap, sp.norm_eps, mw["out_norm"],
+                                   state, torch.bfloat16))
+        sbytes = nseq * mls.heads * mls.dim * (mls.vdim + 1) * 4 * 2
+        add(f"mlstm: gates + recurrence + normaliser + unit norm + gate, fp32 ({tag})", ms,
+            nbytes=n * ld * 4 + n * mls.heads * mls.vdim * (4 + 4 + 2) + sbytes, flops32=4 * n * mls.heads * mls.dim * (mls.vdim + 1),
+            like="retention")
+        rld = 2 * ret.heads * (ret.dim + ret.vdim)
+        qkvg = torch.randn(n, rld, device=device)
+        rstate = rm.cache.ret_state[rsp.layers.index(ret)]
+        ms = timer(lambda: Q.retention(qkvg, batch, ret.heads, ret.dim, ret.vdim, ret.rot_dims, rw["inv_freq"], rw["decay"],
+                                       rsp.norm_eps, rstate, torch.bfloat16))
+        add(f"radanex retention: rotary + recurrence + unit norm + gate, fp32 ({tag})", ms,
+            nbytes=n * rld * 4 + n * ret.heads * ret.vdim * (4 + 4 + 2) + nseq * ret.heads * ret.dim * ret.vdim * 8,
+            flops32=4 * n * ret.heads * ret.dim * ret.vdim)
+        # the attention kinds
+        for l, w, name in ((att, aw, f"window {att.window} + blocks of {att.pool}, sink"), (at2, sw, "causal, sigmoid weights")):
+            H, G, D, V = l.heads, l.kv_heads, l.dim, l.vdim
+            cq, ck = H * D, G * D
+            cv = 0 if l.values_are_keys else G * V
+            gate_rows = H if l.gate_kind == 1 else H * V
+            pr = torch.randn(n, cq + ck + cv + gate_rows, device=device)
+            li = sp.layers.index(l)
+            cache, pooled, conv = zm.cache.kv_cache[li], zm.cache.pool_cache[li], zm.cache.conv_state[li]
+            ms = timer(lambda: Q.attention_prep(pr, w.get("bias_in"), batch, H, G, D, V, l.rot_dims, w["inv_freq"], l.rot_mag,
+                                                l.values_are_keys, l.taps, w.get("conv_w"), conv, torch.bfloat16))
+            add(f"attention prep: bias{' + conv' if l.taps > 1 else ''} + rotary -> q, key|value rows ({name}; {tag})", ms,
+                nbytes=n * (cq + ck + cv) * 4 + n * (cq + G * (D + V)) * 2)
+            q, kv = Q.attention_prep(pr, w.get("bias_in"), batch, H, G, D, V, l.rot_dims, w["inv_freq"], l.rot_mag,
+                                     l.values_are_keys, l.taps, w.get("conv_w"), conv, torch.bfloat16)
+            mode = S.UMBS_ATTN_SOFTMAX_SINK if l.attn_mode == "softmax_sink" else S.UMBS_ATTN_SIGMOID
+            gate = pr[:, cq + ck + cv:]
+            ms = timer(lambda: Q.cached_attention(q, kv, cache, batch, H, G, D, V, l.scale, mode=mode, window=l.window, pool=l.pool,
+                                                  pool_cache=pooled, head_bias=w.get("head_bias"), gate=gate,
+                                                  gate_per_head=l.gate_kind == 1, append=False))
+            win = l.window if l.window > 0 else 1 << 30
+            seen = lambda p: min(p + 1, win) + (max(0, p - win + 1) // l.pool if l.pool else 0)
+            keys = sum(seen(p) for p in range(pos0, pos0 + per)) * nseq
+            kv_bytes = n * G * (D + V) * 2 if n == T else nseq * seen(pos0) * G * (D + V) * 2
+            add(f"cached attention, {name}, fp32 scores ({tag})", ms, nbytes=n * H * (D + V) * 2 + kv_bytes,
+                flops32=2 * keys * H * (D + V), like="window attention over per-head keys" if n == T else "latent attention")
+        # Radanex's attention the same way
+        R = lat.kv_rank
+        lring = rm.cache.ring[rsp.layers.index(lat)]
+        keys = sum(min(p + 1, lat.window) for p in range(pos0, pos0 + per)) * nseq
+        if n == T:
+            hd, hvv = lat.heads * lat.dim, lat.heads * lat.vdim
+            qh, kvh = torch.randn(n, hd, **bf), torch.randn(n, hd + hvv, **bf)
+            ms = timer(lambda: Q.window_attention(qh, kvh[:, :hd], kvh[:, hd:], batch, lat.heads, lat.window, lat.scale))
+            add(f"radanex window attention over per-head keys, window {lat.window}, fp32 scores ({tag})", ms,
+                nbytes=n * (2 * hd + 2 * hvv) * 2, flops32=2 * keys * lat.heads * (lat.dim + lat.vdim))
+        else:
+            qa, c = torch.randn(n, lat.heads * R, device=device), torch.randn(n, R, **bf)
+            ms = timer(lambda: Q.latent_attention(qa, c, lring, batch, lat.heads, lat.window, lat.scale, append=False))
+            add(f"radanex latent attention, window {lat.window}, fp32 scores ({tag})", ms,
+                nbytes=n * lat.heads * R * 6 + keys * R * 2, flops32=4 * keys * lat.heads * R)
+    return rows, how
+
+
+def run_zedotar(args):
+    from . import _lib_seq
+    device = "cuda:0"
+    timer = Timer(device)
+    hbm, tflops, how = _peaks()
+    sizes, table = [], None
+    launches0 = _lib_seq.load().umbs_launch_count()
+    for width in (1024, 2048):
+        layers, prompt, ctx = 8, 2048, 512
+        zm, z = bench_zedotar(width, layers, device, prompt, ctx, (1, 8, 64), timer)
+        rm, r = bench_radanex(width, layers, device, prompt, ctx, (1, 8, 64), timer)
+        sizes.append({"width": width, "layers": layers, "zedotar_bf16": {k: round(v, 3) for k, v in z.items()},
+                      "radanex_bf16": {k: round(v, 3) for k, v in r.items()}})
+        if width == 2048:
+            table, _ = kernel_table_zedotar(zm, rm, device, timer)
+        del zm, rm
+        torch.cuda.empty_cache()
+    launches = _lib_seq.load().umbs_launch_count() - launches0
+    head = sizes[-1]["zedotar_bf16"]
+    line = {"metric": "decode tokens/sec at batch 64 (Zedotar bf16, width 2048, 8 layers, synthetic weights)",
+            "value": head["decode_b64_tok_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic", "vs_baseline": None, "gpu_launches": int(launches),
+            "config": {"name": "zedotar", "workload": "prefill 1 x 2048 and 4 x 2048 tokens; decode at batch 1 / 8 / 64 behind a "
+                       "512-token context; Radanex bf16 of the same width, depth and active feed-forward size beside it",
                        "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": how},
                        "l2": "whole-model runs stream more than L2 per step; kernel table flushes L2 between runs"},
             "sizes": sizes, "kernels": table}
