@@ -21,9 +21,10 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from umbrella_b200.speculation.auto_engine import AutoEngine  # noqa: E402
 
 ap = argparse.ArgumentParser()
-ap.add_argument("--config", default=None, help="an engine config such as configs/b200_batch_radanex.json")
+ap.add_argument("--config", default=None, help="an engine config such as configs/b200_batch_radanex.json or configs/b200_batch_zedotar.json")
 ap.add_argument("--model", default=None)
-ap.add_argument("--synthetic-width", type=int, default=0, help="build a synthetic Radanex config of this width instead")
+ap.add_argument("--synthetic-width", type=int, default=0, help="build a synthetic config of this width instead")
+ap.add_argument("--family", default="radanex", choices=["radanex", "zedotar"], help="family of the synthetic config")
 ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
 ap.add_argument("--prompts", type=int, default=8)
 ap.add_argument("--prompt-len", type=int, default=128)
@@ -37,9 +38,10 @@ if args.config:
 if args.model:
     config["model"] = args.model
 if args.synthetic_width:
-    from umbrella_b200.seq_bench import radanex_config
-    d = tempfile.mkdtemp(prefix="radanex_synth_")
-    json.dump(radanex_config(args.synthetic_width), open(os.path.join(d, "config.json"), "w"))
+    from umbrella_b200 import seq_bench
+    d = tempfile.mkdtemp(prefix=args.family + "_synth_")
+    make = seq_bench.zedotar_config if args.family == "zedotar" else seq_bench.radanex_config
+    json.dump(make(args.synthetic_width), open(os.path.join(d, "config.json"), "w"))
     config.update(model=d, synthetic=True)
 engine = AutoEngine.from_config("cuda:0", **config)
 engine.initialize()

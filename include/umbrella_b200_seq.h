@@ -274,7 +274,7 @@ int umbs_kv_pool(int dtype, const void* kv, const void* kv_cache, int kv_len, vo
  * b pool + pool - 1 <= i - window.  Tokens j >= seq_pos0 are read from kv, older ones from kv_cache, blocks from pool_cache.
  * mode: UMBS_ATTN_*; scores (q . k) scale (+ head_bias[h] for the sigmoid), fp32 throughout.  The output of head h is
  * multiplied by sigmoid(gate[t ldg + h]) (gate_per_head) or element by element by sigmoid(gate[t ldg + h vdim + c]);
- * gate may be NULL.  out: `dtype` [n_tokens, heads vdim].  dim, vdim <= 128 (umbs_window_attention_fits).
+ * gate may be NULL.  out: `dtype` [n_tokens, heads vdim].  dim, vdim <= 256, else UMB_ERR_UNSUPPORTED.
  * split_scratch (optional, fp32): a decode step (one token per sequence) spreads every row's keys over several blocks
  * and merges their partial sums; it needs n_tokens heads n (vdim + 2) floats there and runs unsplit with less. */
 int umbs_cached_attention(int dtype, int mode, const void* q, const void* kv, const void* kv_cache, int kv_len,

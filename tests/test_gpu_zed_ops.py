@@ -301,3 +301,26 @@ def test_mlstm_long_sequences_cut_into_segments():
     ref = mlstm_reference(full, bias, H, D, V, cap, 1e-5, norm_w)[-1:]
     out = K.mlstm(f32(extra), f32(bias), K.RaggedBatch([(0, 1, lens[0], 0)], DEV), H, D, V, cap, 1e-5, f32(norm_w), state)
     assert err(out, ref) < 3e-5
+
+
+@pytest.mark.parametrize("D,V,mode", [(160, 200, "sink"), (256, 256, "sigmoid"), (72, 136, "softmax")])
+def test_attention_with_large_and_uneven_heads(D, V, mode):
+    """Heads above 128 (several passes over the key tile's dimensions, wider value tiles, more elements per lane in
+    decode steps) and sizes that are no multiple of 32."""
+    H, G, n = 2, 1, 90
+    if mode == "sigmoid":
+        V = D
+    q, k, v = rnd(n, H, D, seed=51, scale=0.5), rnd(n, G, D, seed=52, scale=0.5), rnd(n, G, V, seed=53)
+    if mode == "sigmoid":
+        v = k.clone()
+        pb = torch.tensor([-3.0, -2.0], dtype=torch.float64)
+        ref = O.sigmoid_attention(q, k, v, 0.1, pb)
+        kw = dict(window=0, pool=0, head_bias=pb)
+    else:
+        ref = O.pooled_window_attention(q, k, v, 24, 8, 0.1) if mode == "sink" else None
+        kw = dict(window=24, pool=8)
+    for plan in ([n], [n - 20] + [1] * 20, [33, 2, 55]):
+        got = run_attention(q, k, v, plan, H=H, G=G, mode=mode, scale=0.1, **kw)
+        if ref is None:                                 # plain softmax: no oracle form; every cut must give the same numbers
+            ref = got.double().cpu()
+        assert err(got, ref) < 5e-6, plan[:3]

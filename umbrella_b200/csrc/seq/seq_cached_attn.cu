@@ -224,7 +224,9 @@ static int launch_tiles(const CachedAttnArgs& a, const Batch& b, cudaStream_t st
 
 template <typename T, int MODE>
 static int launch_mode(const CachedAttnArgs& a, const Batch& b, cudaStream_t st) {
-    return a.vdim <= 64 ? launch_tiles<T, 4, MODE>(a, b, st) : launch_tiles<T, 8, MODE>(a, b, st);
+    if (a.vdim <= 64) return launch_tiles<T, 4, MODE>(a, b, st);
+    if (a.vdim <= 128) return launch_tiles<T, 8, MODE>(a, b, st);
+    return launch_tiles<T, 16, MODE>(a, b, st);
 }
 
 template <typename T>
@@ -244,12 +246,12 @@ static int launch_any(int mode, const CachedAttnArgs& a, const Batch& b, cudaStr
 // keys w, w + 8, ... of the run, lanes striding over the head's dimensions, with its own running (maximum, sum, output).
 // The warps' triples are merged in shared memory; one split writes the output itself, several leave their triples in
 // `part` [(token, head), split, vdim + 2] for cached_attention_merge_kernel.
-constexpr int kCdWarps = 8, kCdMaxPerLane = 4;        // dim, vdim <= 128
+constexpr int kCdWarps = 8, kCdMaxPerLane = 8;        // dim, vdim <= 256
 
 template <typename T, int MODE>
 __global__ void __launch_bounds__(32 * kCdWarps) cached_attention_decode_kernel(CachedAttnArgs a, Batch b, int n_split,
                                                                                 float* __restrict__ part) {
-    __shared__ float sm_o[kCdWarps][128];
+    __shared__ float sm_o[kCdWarps][32 * kCdMaxPerLane];
     __shared__ float sm_ml[kCdWarps][2];
     const int split = blockIdx.x, h = blockIdx.y, s = blockIdx.z;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -364,7 +366,7 @@ __global__ void cached_attention_merge_kernel(CachedAttnArgs a, int n_split, con
 template <typename T, int MODE>
 static int launch_decode(const CachedAttnArgs& a, const Batch& b, int n_split, float* part, cudaStream_t st) {
     cached_attention_decode_kernel<T, MODE><<<dim3(n_split, a.heads, b.n_seqs), 32 * kCdWarps, 0, st>>>(a, b, n_split, part);
-    if (n_split > 1) cached_attention_merge_kernel<T, MODE><<<b.n_tokens * a.heads, 128, 0, st>>>(a, n_split, part);
+    if (n_split > 1) cached_attention_merge_kernel<T, MODE><<<b.n_tokens * a.heads, a.vdim <= 128 ? 128 : 256, 0, st>>>(a, n_split, part);
     return 0;
 }
 
@@ -390,7 +392,7 @@ extern "C" int umbs_cached_attention(int dtype, int mode, const void* q, const v
     if (batch->n_tokens <= 0) return 0;
     if (heads < 1 || kv_heads < 1 || heads % kv_heads != 0 || kv_len < 1) return UMB_ERR_ARG;
     if (pool > 0 && (window <= 0 || pool_cache == nullptr || pool_len < 1)) return UMB_ERR_ARG;
-    if (!umbs_window_attention_fits(dim, vdim)) return UMB_ERR_UNSUPPORTED;
+    if (dim < 1 || vdim < 1 || dim > 256 || vdim > 256) return UMB_ERR_UNSUPPORTED;      // tiles and lanes are sized for heads up to 256
     cudaStream_t st = (cudaStream_t)stream;
     CachedAttnArgs a{q, kv, kv_cache, pool_cache, kv_len, pool_len, heads, kv_heads, dim, vdim, window, pool, scale,
                      head_bias, gate, ldg, gate_per_head, out};

@@ -276,10 +276,11 @@ extern "C" int umbs_mlstm(int dtype, const float* proj, int64_t ld, const float*
     int n_seg = 1, seg_len = batch->max_seq_len;
     const int base_blocks = batch->n_seqs * heads * ((V1 + 31) / 32);
     const size_t per_seg = (size_t)batch->n_seqs * heads * ((size_t)dim * V1 + 1) * sizeof(float);      // states + decay products
-    if (seg_scratch != nullptr && base_blocks <= 148 && batch->max_seq_len >= 128) {
-        int want = std::min((592 + base_blocks - 1) / base_blocks, batch->max_seq_len / 64);
+    // about four blocks per SM run side by side; two passes pay from three segments on (2 / n_seg of the single walk)
+    if (seg_scratch != nullptr && base_blocks * 3 <= 592 && batch->max_seq_len >= 192) {
+        int want = std::min(592 / base_blocks, batch->max_seq_len / 64);
         want = (int)std::min<size_t>(want, seg_bytes / per_seg);
-        if (want >= 2) {
+        if (want >= 3) {
             seg_len = ((batch->max_seq_len + want - 1) / want + 15) & ~15;
             n_seg = (batch->max_seq_len + seg_len - 1) / seg_len;
         }

@@ -149,24 +149,32 @@ __global__ void attention_prep_kernel(const float* __restrict__ proj, int64_t ld
         for (int c = threadIdx.x; c < Cv; c += blockDim.x) ko[Ck + c] = from_f32<T>(row[C + c] + (bias ? bias[C + c] : 0.f));
 }
 
-// One block per (block of tokens completed by the step, sequence): the fp32 mean, in position order, of the block's kv
-// rows as the cache holds them.
+// One block per (block of tokens completed by the step, sequence, 256 columns): the fp32 mean, in position order, of the
+// block's kv rows as the cache holds them.  Eight rows are loaded ahead of the additions, which stay in position order.
 template <typename T>
 __global__ void kv_pool_kernel(const T* __restrict__ kv, const T* __restrict__ kv_cache, int kv_len, T* __restrict__ pool_cache,
                                int pool_len, Batch b, int row, int pool) {
     const int s = blockIdx.y, pos0 = b.seq_pos0[s], len = b.seq_len[s], start = b.seq_start[s], slot = b.seq_slot[s];
     const int blk = pos0 / pool + blockIdx.x;                    // first block whose last token is in the step, onwards
     if ((int64_t)(blk + 1) * pool > (int64_t)pos0 + len || blk >= pool_len) return;
-    const float inv = 1.f / (float)pool;
-    for (int c = threadIdx.x; c < row; c += blockDim.x) {
-        float acc = 0.f;
-        for (int j = blk * pool; j < (blk + 1) * pool; ++j) {
-            const T* src = j >= pos0 ? kv + (int64_t)(start + j - pos0) * row
-                                     : kv_cache + ((int64_t)slot * kv_len + j % kv_len) * row;
-            acc += to_f32(src[c]);
-        }
-        pool_cache[((int64_t)slot * pool_len + blk) * row + c] = from_f32<T>(acc * inv);
+    const int c = blockIdx.z * blockDim.x + threadIdx.x;
+    if (c >= row) return;
+    auto at = [&](int j) -> float {
+        const T* src = j >= pos0 ? kv + (int64_t)(start + j - pos0) * row : kv_cache + ((int64_t)slot * kv_len + j % kv_len) * row;
+        return to_f32(src[c]);
+    };
+    float acc = 0.f;
+    const int j0 = blk * pool;
+    int j = 0;
+    for (; j + 8 <= pool; j += 8) {
+        float x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) x[u] = at(j0 + j + u);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc += x[u];
     }
+    for (; j < pool; ++j) acc += at(j0 + j);
+    pool_cache[((int64_t)slot * pool_len + blk) * row + c] = from_f32<T>(acc / (float)pool);
 }
 
 }  // namespace umbs
@@ -211,7 +219,7 @@ extern "C" int umbs_attention_prep(int dtype, const float* proj, int64_t ld, con
     const int C = (heads + kv_heads) * dim;
     const size_t smem = ((size_t)C + rot_dims + 2) * sizeof(float);
     if (smem > 48 * 1024) return UMB_ERR_UNSUPPORTED;
-    const int threads = C >= 2048 ? 256 : 128;
+    const int threads = C >= 1024 ? 256 : 128;
     UMBS_DISPATCH_T(dtype, attention_prep_kernel<T><<<batch->n_tokens, threads, smem, st>>>(
                                proj, ld, bias, *batch, heads, kv_heads, dim, vdim, values_are_keys, taps, conv_w, conv_state, slots,
                                rot_dims, inv_freq, rot_mag, (T*)q, (T*)kv));
@@ -224,8 +232,8 @@ extern "C" int umbs_kv_pool(int dtype, const void* kv, const void* kv_cache, int
     if (batch->n_tokens <= 0 || pool <= 0) return 0;
     if (kv_len < pool) return UMB_ERR_ARG;               // a block's older tokens must still sit in the cache
     cudaStream_t st = (cudaStream_t)stream;
-    const dim3 grid(batch->max_seq_len / pool + 1, batch->n_seqs);
-    UMBS_DISPATCH_T(dtype, kv_pool_kernel<T><<<grid, 128, 0, st>>>((const T*)kv, (const T*)kv_cache, kv_len, (T*)pool_cache,
+    const dim3 grid(batch->max_seq_len / pool + 1, batch->n_seqs, (row + 255) / 256);
+    UMBS_DISPATCH_T(dtype, kv_pool_kernel<T><<<grid, 256, 0, st>>>((const T*)kv, (const T*)kv_cache, kv_len, (T*)pool_cache,
                                                                    pool_len, *batch, row, pool));
     count_launches(1);
     return (int)cudaGetLastError();

@@ -61,10 +61,10 @@ def spec_from_config(cfg: dict) -> SeqModelSpec:
     layers = []
     for entry in cfg["layers"]:
         kind, mx = entry["type"], entry["mixer"]
-        l = SeqLayerSpec(heads=int(mx["heads"]), dim=int(mx["dim"]), vdim=int(mx["vdim"]), form="prenorm", norm_offset=1.0,
+        l = SeqLayerSpec(heads=int(mx["heads"]), dim=int(mx["dim"]), vdim=int(mx.get("vdim", mx["dim"])), form="prenorm", norm_offset=1.0,
                          shift=False, depth_average=False)
         if kind == "attention":
-            l.mixer, l.kv_heads, l.scale = "cached_attention", int(mx["kv_heads"]), float(mx["scale"])
+            l.mixer, l.kv_heads, l.scale = "cached_attention", int(mx.get("kv_heads", l.heads)), float(mx["scale"])
             l.attn_mode, l.gate_kind, l.bias = "softmax_sink", 1, True
             mask = mx.get("mask") or {}
             l.window, l.pool = int(mask.get("size", 0)), int(mask.get("pool", 0))
@@ -72,7 +72,7 @@ def spec_from_config(cfg: dict) -> SeqModelSpec:
                 raise ValueError("attention: pooled blocks need a window")
             _rotary(l, mx.get("rot"), "wavelength")
         elif kind == "attention_2":
-            l.mixer, l.kv_heads, l.scale = "cached_attention", int(mx["kv_heads"]), float(mx["scale"])
+            l.mixer, l.kv_heads, l.scale = "cached_attention", int(mx.get("kv_heads", l.heads)), float(mx["scale"])
             l.attn_mode, l.gate_kind, l.bias, l.head_bias = "sigmoid", 2, True, True
             l.values_are_keys, l.taps, l.window = True, int(mx.get("conv", 1)), 0
             if l.vdim != l.dim:
