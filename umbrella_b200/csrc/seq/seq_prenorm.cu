@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
+#include <algorithm>
 #include <stdint.h>
 
 #include "seq_internal.h"
@@ -219,7 +220,8 @@ extern "C" int umbs_attention_prep(int dtype, const float* proj, int64_t ld, con
     const int C = (heads + kv_heads) * dim;
     const size_t smem = ((size_t)C + rot_dims + 2) * sizeof(float);
     if (smem > 48 * 1024) return UMB_ERR_UNSUPPORTED;
-    const int threads = C >= 1024 ? 256 : 128;
+    // a small step (decoding) has few blocks: spread a token's channels over up to 1024 threads
+    const int threads = batch->n_tokens <= 64 ? std::min(1024, (C + 31) / 32 * 32) : (C >= 1024 ? 256 : 128);
     UMBS_DISPATCH_T(dtype, attention_prep_kernel<T><<<batch->n_tokens, threads, smem, st>>>(
                                proj, ld, bias, *batch, heads, kv_heads, dim, vdim, values_are_keys, taps, conv_w, conv_state, slots,
                                rot_dims, inv_freq, rot_mag, (T*)q, (T*)kv));
