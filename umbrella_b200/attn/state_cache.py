@@ -31,6 +31,7 @@ class SequenceStateCache:
         self.slots = 0
         # tokens per sequence that the growing parts (windowless key/value rows, pooled-block tables) hold
         self.capacity = int(max_length or capacity or 512)
+        self._growing = any(l.mixer == "cached_attention" and (l.window <= 0 or l.pool > 0) for l in spec.layers)
         n = len(spec.layers)
         self.kv_cache: list[torch.Tensor | None] = [None] * n
         self.pool_cache: list[torch.Tensor | None] = [None] * n
@@ -58,7 +59,7 @@ class SequenceStateCache:
 
     def reserve_length(self, tokens: int):
         """Make sure a sequence of ``tokens`` tokens fits the growing parts (doubling the capacity when it does not)."""
-        if tokens <= self.capacity:
+        if tokens <= self.capacity or not self._growing:
             return
         if self.max_length is not None and tokens > self.max_length:
             raise RuntimeError(f"sequence longer than max_length {self.max_length}")

@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(256) cached_attention_kernel(CachedAttnArgs a,
             for (int jj = 0; jj < 4; ++jj) sc[i][jj] = 0.f;
         for (int d0 = 0; d0 < dim; d0 += kCaD) {
             const int dc = min(kCaD, dim - d0);
-            __syncthreads();                          // the previous pass or tile is consumed (first time round: Qs is written)
+            __syncthreads();                          // the previous pass or tile is consumed (the very first time: Qs is written)
             for (int i = tid; i < kCaK * dc; i += 256) {
                 const int kk = i / dc, d = i - kk * dc, j = base + kk;
                 float val = 0.f;

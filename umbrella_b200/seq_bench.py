@@ -61,7 +61,7 @@ def zedotar_config(width: int, layers: int = 8) -> dict:
     """A Zedotar config with the layer sizes of a model of this width: mLSTM layers with a windowed attention layer as
     every fourth and a convolved sigmoid-attention layer as the last; dense feed-forward of the width Radanex activates."""
     heads = width // 128
-    rot = dict(dims=64, base=5e5)
+    rot = dict(dims=64, base=1e6)
     mls = dict(type="mlstm", mixer=dict(heads=heads, dim=64, vdim=128, gate_cap=15.0))
     att = dict(type="attention", mixer=dict(heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, scale=128 ** -0.5,
                                             mask=dict(size=1024, pool=64),
