@@ -161,3 +161,52 @@ def test_greedy_generation_through_engine_and_queue(mixed):
     eng.update_generation_args(temperature=0.8, topk=8, topp=0.9)
     sampled = eng.generate_batch(prompts[:2], max_new_tokens=5)
     assert all(len(x) == 5 and all(0 <= y < cfg["vocab"] for y in x) for x in sampled)
+
+
+def _random_config(rng):
+    """Sizes, head counts, layer order, windows, block sizes, taps and constants drawn at random (odd ones included)."""
+    layers = []
+    for _ in range(rng.randint(3, 5)):
+        kind = rng.choice(["attention", "attention_2", "mlstm"])
+        heads, dim, ff = rng.choice([1, 2, 3, 6, 8]), rng.choice([8, 24, 40, 80, 128]), rng.choice([None, 100, 144])
+        if kind == "mlstm":
+            layers.append(dict(type=kind, heads=heads, dim=dim, vdim=rng.choice([8, 33, 64, 96]), gate_cap=rng.choice([5.0, 20.0]), ff=ff))
+            continue
+        kv = rng.choice([d for d in range(1, heads + 1) if heads % d == 0])
+        rd = rng.choice([0, dim, dim // 4 * 2])
+        rot = None
+        if rd and kind == "attention":
+            rot = dict(dims=rd, base=rng.choice([100.0, 1e4]), scaling=rng.choice(
+                [None, dict(factor=rng.choice([2.0, 8.0]), low=rng.choice([0.5, 1.0]), high=rng.choice([2.0, 4.0]), original=rng.choice([16, 64]))]))
+        elif rd:
+            rot = dict(dims=rd, base=rng.choice([100.0, 1e4]), scaling=rng.choice(
+                [None, dict(factor=rng.choice([2.0, 16.0]), original=rng.choice([32, 128]), fast=rng.choice([8.0, 32.0]), slow=rng.choice([1.0, 2.0]))]))
+        if kind == "attention":
+            layers.append(dict(type=kind, heads=heads, kv_heads=kv, dim=dim, vdim=rng.choice([dim, 16, 100]), window=rng.choice([3, 17, 50, 1000]),
+                               pool=rng.choice([0, 2, 5, 16]), scale=dim ** -0.5, rot=rot, ff=ff))
+        else:
+            layers.append(dict(type=kind, heads=heads, kv_heads=kv, dim=dim, vdim=dim, conv=rng.choice([1, 2, 5]), scale=dim ** -0.5, rot=rot, ff=ff))
+    return dict(width=rng.choice([72, 96, 200]), vocab=rng.choice([130, 301]), eps=rng.choice([1e-5, 1e-6]), softcap=rng.choice([None, 10.0]),
+                layers=layers)
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13])
+def test_random_configurations(seed):
+    """Nothing rests on one model's sizes: random configurations, a ragged batch prefilled and decoded together."""
+    import random
+    cfg = _random_config(random.Random(seed))
+    t = H.random_tensors(cfg, seed=seed)
+    om, pm = H.oracle_model(cfg, t), H.product_model(cfg, t, torch.float32, max_tokens=32)
+    seqs = [toks(n, cfg["vocab"], seed + n) for n in (150, 41, 97)]
+    refs = [O.forward(om, s) for s in seqs]
+    slots = [pm.cache.alloc_slot() for _ in seqs]
+    cuts = [len(s) - 25 for s in seqs]
+    out = pm.forward([(sl, s[:c], range(c)) for sl, s, c in zip(slots, seqs, cuts)])
+    got = [[out[sum(cuts[:i]):sum(cuts[:i + 1])]] for i in range(3)]
+    for d in range(25):
+        o = pm.forward([(sl, [s[c + d]], [0]) for sl, s, c in zip(slots, seqs, cuts)])
+        for i in range(3):
+            got[i].append(o[i:i + 1])
+    for i in range(3):
+        rows = H.row_errs(torch.cat(got[i]), refs[i])
+        assert float(rows.median()) < 1e-5 and float(rows.max()) < 3e-4, (seed, i)       # a row whose read-out nearly cancels strays
