@@ -10,6 +10,10 @@
  * Conventions as in umbrella_b200.h: plain device pointers, sizes, a cudaStream_t (as void*); no allocation,
  * no host synchronisation, no default-stream use.  0 = ok, negative = UMB_ERR_*, positive = cudaError_t.
  *
+ * Models of the pre-norm form (UMBS_FORM_PRENORM) also keep what their mixers need in the slot: the key | value rows of
+ * cached attention (a ring for a window, every token without one), one mean key | value row per block of older tokens,
+ * the last projected rows in front of a short convolution, and the matrix memory of mLSTM layers.
+ *
  * The building blocks are exported on their own (umbs_group_norm_shift, umbs_retention, umbs_latent_attention,
  * umbs_moe_route, umbs_gemm, umbs_depth_mix ...), each with its constants as arguments, and umbs_forward chains
  * them for a model described by umbs_model_t.  Numerics: norms, rotary angles, attention scores and weights,

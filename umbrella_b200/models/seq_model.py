@@ -198,7 +198,12 @@ class SeqStateModel:
         retention: q, k [heads dim, width]; v, g [heads vdim, width].
         latent attention: dq [q_rank, width], dq_norm, uq [heads dim, q_rank], dkv [kv_rank, width], dkv_norm,
             uk [heads dim, kv_rank], uv [heads vdim, kv_rank].
-        feed-forward: router [experts, width]; experts: list of (gate, up, down); shared: (gate, up, down)."""
+        cached attention: q [heads dim, width], k [kv_heads dim, width], v [kv_heads vdim, width] (unless the values are
+            the keys), g [heads or heads vdim, width] (by gate_kind); q_b, k_b, v_b (biases); q_conv, k_conv [channels, taps];
+            pb [heads] (score bias).
+        mlstm: q, k [heads dim, width]; v, g [heads vdim, width]; i, f [heads, width] with i_b, f_b [heads]; out_norm [heads vdim].
+        pre-norm layers: norm2 [width] when they have a feed-forward.
+        feed-forward: router [experts, width]; experts: list of (gate, up, down); shared (or dense): (gate, up, down)."""
         l = self.spec.layers[idx]
         d = dict(norm=self._f32(w["norm"]), o=self._act(w["o"]))
         if l.form == "prenorm":
